@@ -1,4 +1,4 @@
-// Instruction-fetch capacity probe for sm_100a: a straight-line block of KB kilobytes of SASS is executed R times by one
+// Instruction-fetch capacity probe for sm_100a: a straight-line block of KB kilobytes of machine code is executed R times by one
 // warp (or several) per SM; cycles per instruction vs block size show where the L0 / L1 / L1.5 instruction caches end.
 //   nvcc -O3 -gencode arch=compute_100a,code=sm_100a -o tools/icache_bench tools/icache_bench.cu
 #include <cstdio>

@@ -1,4 +1,4 @@
-// Legacy tensor path (mma.sync.m16n8k16 f16 -> f32, SASS HMMA.16816.F32) on sm_100a: latency and issue rate per SM
+// Legacy tensor path (mma.sync.m16n8k16 f16 -> f32) on sm_100a: latency and issue rate per SM
 // sub-partition, as a function of independent accumulator chains (ILP) and warps per sub-partition.
 //   nvcc -O3 -gencode arch=compute_100a,code=sm_100a -o tools/mmabench tools/mmabench.cu && tools/mmabench
 #include <cstdio>
