@@ -28,6 +28,7 @@
 #include <algorithm>
 #include "dsk_kernels.cuh"
 #include "dsk_mega.cuh"
+#include "dsk_hybrid.cuh"
 
 using namespace dsk;
 
@@ -128,8 +129,11 @@ struct Uploader {
   double seconds = 0;
 };
 
+namespace hyb { struct Model; struct State; }   // layer-list model family (dsk_hybrid_host.cuh)
+
 struct dsk_model {
   dsk_config c;
+  hyb::Model* hy = nullptr;    // set: a layer-list model; the DeepSeek fields below are unused
   int head_dim = 0;
   int rank = 0, n_ranks = 1;
   int expert_first = 0, expert_count = 0;
@@ -165,6 +169,7 @@ struct dsk_model {
 
 struct dsk_state {
   dsk_model* m = nullptr;
+  hyb::State* hy = nullptr;
   float *x = nullptr, *xb2 = nullptr, *hbk = nullptr, *hbs = nullptr, *q_a = nullptr, *q = nullptr, *kv_a = nullptr,
         *kv_b = nullptr, *q_c = nullptr, *moe_logits = nullptr, *moe_scores = nullptr, *act_w = nullptr, *logits = nullptr, *partial = nullptr;
   int* act = nullptr;
@@ -194,6 +199,21 @@ struct dsk_state {
   int n_tail = 1;                       // stages after the last layer (LM head [+ arg-max exchange]): skipped by HYDRATE_KV_CACHE
   float* logits_src = nullptr;          // where the full logits of the last forward live (tp: the exchange allocation)
 };
+
+namespace hyb {
+static dsk_model* model_create(const dsk_hybrid_config* cfg, const dsk_layer_spec* layers, int rank, int n_ranks);
+static void model_free(dsk_model* m);
+static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape[4], const void* data, size_t nbytes, int on_dev);
+static int finalize(dsk_model* m);
+static double active_bytes(const dsk_model* m);
+static int launches_per_token(const dsk_model* m);
+static dsk_state* state_create(dsk_model* m);
+static void state_free(dsk_state* s);
+static int state_reset(dsk_state* s);
+static int forward_chunk(dsk_model* m, dsk_state* s, const int32_t* tokens, int n, int pos0, const int32_t* want, int n_want,
+                         float* host_logits, float* host_layers);
+static int decode_greedy(dsk_model* m, dsk_state* s, int start_pos, int n_steps, int32_t* out_tokens, float* elapsed_ms);
+}  // namespace hyb
 
 static size_t disk_row_bytes(int quant, int cols) {
   switch (quant) {
@@ -409,6 +429,7 @@ static void uploader_release(Uploader& u) {
 
 extern "C" void dsk_model_destroy(dsk_model* m) {
   if (!m) return;
+  if (m->hy) hyb::model_free(m);
   uploader_release(m->up);
   if (m->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(m->comm);
   for (int q = 0; q < kMaxRanks; q++) if (m->xchg_peer[q] && q != m->rank) cudaIpcCloseMemHandle(m->xchg_peer[q]);
@@ -588,6 +609,7 @@ extern "C" int dsk_upload_tensor(dsk_model* m, const char* name, int dtype, cons
                                  size_t nbytes, int src_on_device) {
   if (need_device()) return -1;
   if (!m || !name || !data || !shape) return fail(-1, "bad arguments");
+  if (m->hy) return hyb::upload(m, name, dtype, shape, data, nbytes, src_on_device);
   const dsk_config& c = m->c;
   const int hd = m->head_dim, nope = c.qk_nope_head_dim, mi = c.moe_intermediate_size;
   std::string nm(name);
@@ -654,6 +676,7 @@ extern "C" int dsk_upload_tensor(dsk_model* m, const char* name, int dtype, cons
 extern "C" int dsk_model_finalize(dsk_model* m) {
   if (need_device()) return -1;
   if (!m) return fail(-1, "null model");
+  if (m->hy) return hyb::finalize(m);
   const dsk_config& c = m->c;
   const bool f8 = c.quant == DSK_F8E5M2;
   auto need = [&](const DTensor& t, const char* what, int l) -> int {
@@ -706,6 +729,7 @@ extern "C" int dsk_model_sharding(const dsk_model* m, int* tensor_parallel, int*
 // bpw = 4 / 2 / 1+4/(bs0*bs1) / 84/256 / 110/256, plus the F32 gate, gate bias and norm weights.
 extern "C" double dsk_model_active_bytes_per_token(const dsk_model* m) {
   if (!m) return 0;
+  if (m->hy) return hyb::active_bytes(m);
   const dsk_config& c = m->c;
   double bpw = 4;
   switch (c.quant) {
@@ -748,6 +772,7 @@ static int build_program(dsk_model* m, dsk_state* s);
 
 extern "C" dsk_state* dsk_state_create(dsk_model* m) {
   if (need_device() || !m) return nullptr;
+  if (m->hy) return hyb::state_create(m);
   const dsk_config& c = m->c;
   dsk_state* s = new dsk_state();
   s->m = m;
@@ -791,6 +816,7 @@ extern "C" dsk_state* dsk_state_create(dsk_model* m) {
 extern "C" void dsk_state_destroy(dsk_state* s) {
   if (!s) return;
   if (s->m) s->m->n_states--;
+  if (s->hy) hyb::state_free(s);
   float* bufs[] = {s->x, s->xb2, s->hbk, s->hbs, s->q_a, s->q, s->q_c, s->kv_a, s->kv_b, s->moe_logits, s->moe_scores, s->act_w, s->logits, s->partial};
   for (float* b : bufs) cudaFree(b);
   cudaFree(s->prog); cudaFree(s->att_scratch); cudaFree(s->sync_words); cudaFree(s->tstamp);
@@ -803,6 +829,10 @@ extern "C" void dsk_state_destroy(dsk_state* s) {
 static float* state_buf(dsk_state* s, const char* name, size_t* cap) {
   const dsk_config& c = s->m->c;
   std::string k(name);
+  if (s->hy) {   // layer-list models expose the logits row only; their activations are chunk-shaped (see dsk_forward_chunk)
+    if (k == "logits") { *cap = c.vocab_size; return s->logits; }
+    return nullptr;
+  }
   if (k == "x") { *cap = c.dim; return s->x; }
   if (k == "xb2") { *cap = std::max(std::max(c.dim, c.n_heads * c.v_head_dim), c.use_mla ? c.n_heads * c.kv_lora_rank : 0); return s->xb2; }
   if (k == "q_c" && c.use_mla) { *cap = (size_t)c.n_heads * c.kv_lora_rank; return s->q_c; }
@@ -847,6 +877,7 @@ extern "C" int dsk_state_read_i32(dsk_state* s, const char* buffer, int32_t* dst
 }
 static int kv_ptr(dsk_model* m, int layer, int which, __half** p, size_t* cap) {
   if (!m || layer < 0 || layer >= m->c.n_layers) return fail(-4, "bad layer");
+  if (m->hy) return fail(-4, "layer-list models keep their caches in the state (no fp16 KV rows to read or write)");
   Layer& L = m->layers[layer];
   *p = which == 0 ? L.kcache : L.vcache;
   *cap = m->c.use_mla ? (size_t)m->c.max_seq_len * (which == 0 ? m->c.kv_lora_rank : m->c.qk_rope_head_dim)
@@ -1453,6 +1484,15 @@ extern "C" int dsk_forward(dsk_model* m, dsk_state* s, int token, int pos, int m
   if (token < 0 || token >= c.vocab_size) return fail(-4, "token %d out of range", token);
   if (pos < 0) return fail(-4, "negative pos");
   mode = mode ? 1 : 0;
+  if (m->hy) {   // one-token chunk through the layer-list kernels
+    const int32_t tok = token, w0 = 0;
+    if (hyb::forward_chunk(m, s, &tok, 1, pos, &w0, mode, mode ? host_logits : nullptr, nullptr)) return -2;
+    if (mode && argmax) {
+      CK(cudaMemcpy(s->h_ctrl, s->ctrl, sizeof(Ctrl), cudaMemcpyDeviceToHost));
+      *argmax = (int)(0xFFFFFFFFu - (unsigned)(s->h_ctrl->argmax_key & 0xFFFFFFFFull));
+    }
+    return 0;
+  }
   if (m->n_ranks > 1 && !m->comm) return fail(-3, "n_ranks > 1 but dsk_comm_init() was not called");
   if (ensure_program(m, s)) return -2;
   fill_ctrl(s->h_ctrl, c, token, pos);
@@ -1475,6 +1515,7 @@ extern "C" int dsk_copy_embedding(dsk_model* m, dsk_state* s, int token) {
   if (need_device()) return -1;
   if (!m || !s) return fail(-1, "null model/state");
   if (token < 0 || token >= m->c.vocab_size) return fail(-4, "token %d out of range", token);
+  if (m->hy) return fail(-4, "dsk_copy_embedding: not part of the layer-list path (use dsk_forward_chunk with host_layers)");
   if (ensure_program(m, s)) return -2;
   fill_ctrl(s->h_ctrl, m->c, token, 0);
   set_xchg_base(m, s, 0, 1);
@@ -1490,6 +1531,7 @@ extern "C" int dsk_block_forward(dsk_model* m, dsk_state* s, int layer, int pos,
   if (!m || !s) return fail(-1, "null model/state");
   const dsk_config& c = m->c;
   if (layer < 0 || layer >= c.n_layers) return fail(-4, "bad layer %d", layer);
+  if (m->hy) return fail(-4, "dsk_block_forward: not part of the layer-list path (use dsk_forward_chunk with host_layers)");
   if (pos < 0 || kv_sink < 0 || kv_pos < 0 || kv_pos >= c.max_seq_len || kv_len < 1 || kv_len > c.max_seq_len || kv_sink > kv_len)
     return fail(-4, "block(pos %d, kv_sink %d, kv_pos %d, kv_len %d) does not fit the KV cache (max_seq_len %d)", pos, kv_sink, kv_pos, kv_len, c.max_seq_len);
   if (m->n_ranks > 1 && !m->comm) return fail(-3, "n_ranks > 1 but dsk_comm_init() was not called");
@@ -1516,6 +1558,7 @@ extern "C" int dsk_decode_greedy(dsk_model* m, dsk_state* s, int start_pos, int 
   if (!s->have_logits)
     return fail(-4, "dsk_decode_greedy: the last forward did not produce logits (mode DSK_HYDRATE_KV_CACHE, block or embedding call) — run dsk_forward(..., DSK_OUTPUT_LOGITS) first");
   if ((size_t)n_steps > s->token_log_cap) return fail(-4, "n_steps too large");
+  if (m->hy) return hyb::decode_greedy(m, s, start_pos, n_steps, out_tokens, elapsed_ms);
   const dsk_config& c = m->c;
   if (c.original_max_position > c.max_seq_len && start_pos + n_steps > c.max_seq_len)
     return fail(-4, "decode would run past the KV cache (%d)", c.max_seq_len);
@@ -1649,6 +1692,7 @@ extern "C" int dsk_sample_prob(dsk_model* m, dsk_state* s, int index, float* pro
 extern "C" int dsk_launches_per_forward(const dsk_model* m, int mode) {
   if (!m) return 0;
   (void)mode;
+  if (m->hy) return hyb::launches_per_token(m);
   const dsk_config& c = m->c;
   int cuts = 0;
   if (m->n_ranks > 1 && !m->p2p) for (int l = 0; l < c.n_layers; l++) cuts += m->layers[l].is_moe ? 1 : 0;   // peer-memory mode: one kernel
@@ -1667,6 +1711,7 @@ extern "C" int dsk_comm_unique_id(void* out128) {
   return 0;
 }
 extern "C" int dsk_comm_init(dsk_model* m, const void* nccl_unique_id128) {
+  if (m && m->hy) return fail(-3, "layer-list models run on one GPU");
   if (need_device()) return -1;
   if (!m) return fail(-1, "null model");
   if (m->n_ranks == 1) return 0;
@@ -2097,6 +2142,7 @@ extern "C" int dsk_bench_gemv(int quant, int d, int n, int n_mats, int warmup, i
 // stage-level timeline of one token from the interpreter's own globaltimer stamps (CTA 0)
 // ---------------------------------------------------------------------------------------------------
 extern "C" int dsk_profile_token(dsk_model* m, dsk_state* s, int token, int pos, char* out, size_t cap) {
+  if (m && m->hy) return fail(-4, "dsk_profile_token: the stage timeline belongs to the persistent interpreter");
   if (need_device()) return -1;
   if (!m || !s || !out) return fail(-1, "bad arguments");
   if (ensure_program(m, s)) return -2;
@@ -2136,5 +2182,40 @@ extern "C" int dsk_profile_token(dsk_model* m, dsk_state* s, int token, int pos,
     off += n;
   }
   snprintf(out + off, cap - off, "token total %.1f us over %d stages (CTA 0 timeline)\n", total, s->n_stages);
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// layer-list model family
+// ---------------------------------------------------------------------------------------------------
+#include "dsk_hybrid_host.cuh"
+
+extern "C" dsk_model* dsk_model_create_hybrid(const dsk_hybrid_config* cfg, const dsk_layer_spec* layers, int rank, int n_ranks) {
+  return hyb::model_create(cfg, layers, rank, n_ranks);
+}
+
+extern "C" int dsk_state_reset(dsk_state* s) {
+  if (need_device()) return -1;
+  if (!s) return fail(-1, "null state");
+  if (s->hy) { if (hyb::state_reset(s)) return -2; CK(cudaStreamSynchronize(s->stream)); return 0; }
+  s->last_pos = -1;          // DeepSeek blocks overwrite their KV rows position by position: nothing to clear
+  s->have_logits = false;
+  return 0;
+}
+
+extern "C" int dsk_forward_chunk(dsk_model* m, dsk_state* s, const int32_t* tokens, int n_tokens, int pos0, const int32_t* want,
+                                 int n_want, float* host_logits, float* host_layers) {
+  if (need_device()) return -1;
+  if (!m || !s || !tokens || n_tokens <= 0 || pos0 < 0 || n_want < 0 || (n_want > 0 && !want)) return fail(-1, "bad arguments");
+  if (m->hy) return hyb::forward_chunk(m, s, tokens, n_tokens, pos0, want, n_want, host_logits, host_layers);
+  if (host_layers) return fail(-4, "host_layers: only layer-list models trace their residual stream here (use dsk_block_forward)");
+  int wi = 0;
+  for (int i = 0; i < n_tokens; i++) {   // the hydrate loop of the reference (src/main.cpp:312-319), logits where asked
+    const bool w = wi < n_want && want[wi] == i;
+    if (dsk_forward(m, s, tokens[i], pos0 + i, w ? DSK_OUTPUT_LOGITS : DSK_HYDRATE_KV_CACHE,
+                    w && host_logits ? host_logits + (size_t)wi * m->c.vocab_size : nullptr, nullptr)) return -2;
+    if (w) wi++;
+  }
+  if (wi != n_want) return fail(-4, "wanted rows must be ascending indices into the chunk");
   return 0;
 }

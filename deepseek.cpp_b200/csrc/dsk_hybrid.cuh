@@ -1,0 +1,617 @@
+// dsk_hybrid.cuh — device kernels of the layer-list ("hybrid") model family: models whose config lists, layer by layer, a
+// token mixer (a state-space-duality recurrence or sliding-window latent attention) and an optional routed feed-forward.
+// Unlike the persistent batch-1 interpreter (dsk_mega.cuh) these kernels take a CHUNK of T consecutive tokens of one sequence:
+// T = 1 is a decode step, T > 1 a prefill portion; the same kernels serve both, reading the recurrent state / latent ring
+// cache that the previous chunk left.  Every mechanism is a kernel of its own with its constants as arguments:
+//
+//   embed_rows        token ids -> fp32 residual rows
+//   group_rmsnorm     RMS norm in `groups` equal consecutive parts (groups = 1: plain RMSNorm); can also add its result,
+//                     scaled, into the residual, or write its rows into a ring cache
+//   gemm_tiled        C = A W^T for T > 4 rows (fp32 activations, fp32 or bf16 weights, fp32 accumulate) with fused
+//                     epilogues (residual add, clamped GLU, GELU x per-token embedding) and row gather / scatter / expert tiles
+//   gemv_rows         the same contract for T <= 4 rows: one warp per weight row, 16-byte loads
+//   causal_conv_silu  depthwise causal convolution over the chunk continuing from the carried (taps - 1) inputs, + SiLU
+//   ssd_scan          the state-space recurrence S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x, gated by silu(z)
+//   latent_swa_attn   softmax attention over a sliding window of cached latents with absorbed key up-projection
+//   moe_route         sigmoid scores, selection by score + correction, weights = normalised scores x scale
+//   moe_plan          groups the (token, slot) pairs of a chunk by expert into row tiles for gemm_tiled
+//   moe_combine       residual += alpha * sum_k w_k y_k
+//
+// Numerics: the residual stream, norms, router, softmax, recurrent state, decays, step sizes and gates are fp32 in every mode;
+// DSK_BF16 models keep their matrices in bfloat16 and multiply them with fp32 activations (fp32 accumulate), DSK_F32 models
+// are fp32 throughout (plain FMA, no reduced-precision matrix mode).
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "dsk_kernels.cuh"
+
+namespace dsk {
+namespace hy {
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float gelu_tanh_f(float z) { return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+// log(1 + e^v) without a clamp: beyond 20 the correction term is below half an ulp of v
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {   // red: 33 floats of shared memory; every thread gets the sum
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// conversions at upload: src (fp32 | bf16, row-major rows x cols, pitch src_ld) -> dst (fp32 | bf16).  `tr` > 0 writes the
+// per-head transpose of a (heads*tr) x cols matrix: dst[h][c][d] = src[h*tr + d][c] (absorbed key up-projection).
+// ---------------------------------------------------------------------------------------------------------------------
+template <typename ST, typename DT>
+__global__ void convert_kernel(const ST* __restrict__ src, DT* __restrict__ dst, long long rows, long long cols, int tr) {
+  const long long n = rows * cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    long long o = i;
+    if (tr > 0) {
+      const long long r = i / cols, c = i - r * cols, h = r / tr, d = r - h * tr;
+      o = (h * cols + c) * tr + d;
+    }
+    dst[o] = from_f<DT>(to_f<ST>(src[i]));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// control words of a chunk: ctl[0] = absolute position of the chunk's first token.  Kept in device memory so that a captured
+// decode step can be replayed: advance_ctl moves it on.
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void set_ctl(int* ctl, int pos0) { ctl[0] = pos0; }
+__global__ void advance_ctl(int* ctl, int by) { ctl[0] += by; }
+
+template <typename WT>
+__global__ void embed_rows(const int* __restrict__ tok, const WT* __restrict__ table, int width, float* __restrict__ x) {
+  const int t = blockIdx.x;
+  const WT* row = table + (size_t)tok[t] * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) x[(size_t)t * width + c] = to_f<WT>(row[c]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// RMS norm in groups.  Row t of `in` (n values) is cut into `groups` equal consecutive parts; each part is divided by
+// sqrt(mean(part^2) + eps) and the row is multiplied by w.  mode 0: out[row] = result, where row = (ctl ? ctl[0] : 0) + t,
+// taken modulo `ring` (a ring cache of latents; ring = 0 means rows are not wrapped).  mode 1: out[t] += alpha * result.
+// ---------------------------------------------------------------------------------------------------------------------
+template <typename OT>
+__global__ void __launch_bounds__(256) group_rmsnorm(const float* __restrict__ in, int ld_in, const float* __restrict__ w,
+                                                     OT* __restrict__ out, int ld_out, int n, int groups, float eps, int mode,
+                                                     float alpha, const int* __restrict__ ctl, int ring) {
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const float* x = in + (size_t)t * ld_in;
+  long long orow = t;
+  if (ctl) orow += ctl[0];
+  if (ring > 0) orow %= ring;
+  OT* o = out + (size_t)orow * ld_out;
+  const int gs = n / groups;
+  for (int g = 0; g < groups; g++) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) { const float v = x[g * gs + i]; ss += v * v; }
+    ss = block_sum(ss, red);
+    const float sc = 1.f / sqrtf(ss / (float)gs + eps);
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+      const int c = g * gs + i;
+      const float v = x[c] * sc * w[c];
+      if (mode == 0) o[c] = from_f<OT>(v);
+      else o[c] = from_f<OT>(to_f<OT>(o[c]) + alpha * v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// matrix products
+// ---------------------------------------------------------------------------------------------------------------------
+enum { HEPI_STORE = 0, HEPI_ADD = 1, HEPI_GLU = 2, HEPI_GELU_MUL = 3 };
+
+struct GemmP {
+  const float* A;          // activations, row pitch lda
+  const void* W;           // weights [N][K] row-major, row pitch ldw (float or bf16)
+  const void* W2;          // HEPI_GLU: the "up" matrix (W is the "gate" matrix)
+  float* C;                // row pitch ldc
+  int M, N, K, lda, ldw, ldc;
+  long long sA, sW, sC;    // element strides per blockIdx.z (per-head batches); sW also is the stride between experts
+  const int* a_map;        // logical row i reads A row a_map[i] / a_div (null: row i)
+  int a_div;
+  const int* c_map;        // logical row i writes C row c_map[i] (null: row i)
+  const int* z_expert;     // gemv_rows only: batch z uses expert z_expert[z], A row z / z_adiv, C row z (one row per batch)
+  int z_adiv;
+  const int4* tiles;       // gemm_tiled only: row tiles grouped by expert {expert, first logical row, rows, -}
+  const int* n_tiles;
+  float alpha;             // STORE: C = alpha acc; ADD: C += alpha acc
+  float lim;               // GLU: g = min(gate, lim), u = clamp(up, -lim, lim), C = g sigmoid(1.702 g) (u + 1)
+  const void* aux;         // GELU_MUL: C = gelu_tanh(acc) * aux[aux_row[row] * aux_ld + aux_off + n]
+  const int* aux_row;
+  int aux_ld, aux_off;
+};
+
+template <typename WT, int EPI>
+__device__ __forceinline__ void gemm_epilogue(const GemmP& P, float* __restrict__ crow, int cr, int n, float v, float v2) {
+  if (EPI == HEPI_STORE) crow[n] = P.alpha * v;
+  else if (EPI == HEPI_ADD) crow[n] += P.alpha * v;
+  else if (EPI == HEPI_GLU) {
+    const float g = fminf(v, P.lim), u = fminf(fmaxf(v2, -P.lim), P.lim);
+    crow[n] = g * sigmoid_f(1.702f * g) * (u + 1.f);
+  } else {
+    const WT* aux = reinterpret_cast<const WT*>(P.aux);
+    crow[n] = gelu_tanh_f(v) * to_f<WT>(aux[(size_t)P.aux_row[cr] * P.aux_ld + P.aux_off + n]);
+  }
+}
+
+// 64 x 64 output tile, K in steps of 16, 256 threads with a 4 x 4 micro-tile each; plain fp32 FMA on fp32 activations.
+template <typename WT, int EPI>
+__global__ void __launch_bounds__(256) gemm_tiled(const GemmP P) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  constexpr bool DUAL = EPI == HEPI_GLU;
+  __shared__ __align__(16) float As[BK][BM + 4];
+  __shared__ __align__(16) float Bs[DUAL ? 2 : 1][BK][BN + 4];
+  __shared__ int rowsA[BM], rowsC[BM];
+  const int tid = threadIdx.x;
+  long long aoff = (long long)blockIdx.z * P.sA, woff = (long long)blockIdx.z * P.sW, coff = (long long)blockIdx.z * P.sC;
+  int row0, nrows;
+  if (P.tiles) {
+    if ((int)blockIdx.y >= *P.n_tiles) return;
+    const int4 t = P.tiles[blockIdx.y];
+    woff = (long long)t.x * P.sW;
+    row0 = t.y;
+    nrows = t.z;
+  } else {
+    row0 = blockIdx.y * BM;
+    nrows = min(BM, P.M - row0);
+  }
+  if (tid < BM) {
+    const int i = row0 + tid;
+    const bool ok = tid < nrows;
+    rowsA[tid] = ok ? (P.a_map ? P.a_map[i] / P.a_div : i) : -1;
+    rowsC[tid] = ok ? (P.c_map ? P.c_map[i] : i) : -1;
+  }
+  __syncthreads();
+  const int n0 = blockIdx.x * BN;
+  const WT* __restrict__ W = reinterpret_cast<const WT*>(P.W) + woff;
+  const WT* __restrict__ W2 = DUAL ? reinterpret_cast<const WT*>(P.W2) + woff : nullptr;
+  const float* __restrict__ A = P.A + aoff;
+  const int lr = tid >> 2, lk = (tid & 3) * 4;
+  const int tx = tid & 15, ty = tid >> 4;
+  float acc[4][4], acc2[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) { acc[i][j] = 0.f; acc2[i][j] = 0.f; }
+  const int ar = rowsA[lr];
+  const int wn = n0 + lr;
+  for (int k0 = 0; k0 < P.K; k0 += BK) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int k = k0 + lk + j;
+      As[lk + j][lr] = (ar >= 0 && k < P.K) ? A[(size_t)ar * P.lda + k] : 0.f;
+      const bool wok = wn < P.N && k < P.K;
+      Bs[0][lk + j][lr] = wok ? to_f<WT>(W[(size_t)wn * P.ldw + k]) : 0.f;
+      if (DUAL) Bs[DUAL ? 1 : 0][lk + j][lr] = wok ? to_f<WT>(W2[(size_t)wn * P.ldw + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk++) {
+      const float4 a4 = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+      const float4 b4 = *reinterpret_cast<const float4*>(&Bs[0][kk][tx * 4]);
+      const float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+      if (DUAL) {
+        const float4 c4 = *reinterpret_cast<const float4*>(&Bs[DUAL ? 1 : 0][kk][tx * 4]);
+        const float c[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) acc2[i][j] = fmaf(a[i], c[j], acc2[i][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int cr = rowsC[ty * 4 + i];
+    if (cr < 0) continue;
+    float* crow = P.C + coff + (size_t)cr * P.ldc;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int n = n0 + tx * 4 + j;
+      if (n < P.N) gemm_epilogue<WT, EPI>(P, crow, cr, n, acc[i][j], acc2[i][j]);
+    }
+  }
+}
+
+template <typename WT> struct WVec;
+template <> struct WVec<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&o)[4]) { const float4 v = *reinterpret_cast<const float4*>(p); o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; }
+};
+template <> struct WVec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&o)[8]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) { o[2 * i] = __uint_as_float(w[i] << 16); o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+  }
+};
+
+// M <= 4 rows: one warp per weight row, lanes stride over K with 16-byte loads when pitches and bases allow it.
+template <typename WT, int EPI>
+__global__ void __launch_bounds__(256) gemv_rows(const GemmP P) {
+  constexpr bool DUAL = EPI == HEPI_GLU;
+  constexpr int MR = 4, V = WVec<WT>::N;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, z = blockIdx.y;
+  long long aoff, woff, coff;
+  int M = P.M;
+  if (P.z_expert) {
+    woff = (long long)P.z_expert[z] * P.sW;
+    aoff = (long long)(z / P.z_adiv) * P.lda;
+    coff = (long long)z * P.ldc;
+    M = 1;
+  } else {
+    aoff = (long long)z * P.sA; woff = (long long)z * P.sW; coff = (long long)z * P.sC;
+  }
+  const WT* __restrict__ W = reinterpret_cast<const WT*>(P.W) + woff;
+  const WT* __restrict__ W2 = DUAL ? reinterpret_cast<const WT*>(P.W2) + woff : nullptr;
+  const float* arow[MR];
+  int crow_i[MR];
+#pragma unroll
+  for (int m = 0; m < MR; m++) {
+    const int mm = m < M ? m : 0;
+    const int ar = (!P.z_expert && P.a_map) ? P.a_map[mm] / P.a_div : mm;
+    arow[m] = P.A + aoff + (size_t)ar * P.lda;
+    crow_i[m] = (!P.z_expert && P.c_map) ? P.c_map[mm] : mm;
+  }
+  const bool vec = (P.K % V == 0) && (P.ldw % V == 0) && (P.lda % 4 == 0) && ((woff * (long long)sizeof(WT)) % 16 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(P.W) | (DUAL ? reinterpret_cast<uintptr_t>(P.W2) : 0)) % 16 == 0) &&
+                   (reinterpret_cast<uintptr_t>(P.A + aoff) % 16 == 0);
+  for (int n = blockIdx.x * 8 + warp; n < P.N; n += gridDim.x * 8) {
+    float acc[MR] = {0.f, 0.f, 0.f, 0.f}, acc2[MR] = {0.f, 0.f, 0.f, 0.f};
+    const WT* w = W + (size_t)n * P.ldw;
+    const WT* w2 = DUAL ? W2 + (size_t)n * P.ldw : nullptr;
+    if (vec) {
+      for (int k = lane * V; k < P.K; k += 32 * V) {
+        float wv[V], wv2[V];
+        WVec<WT>::load(w + k, wv);
+        if (DUAL) WVec<WT>::load(w2 + k, wv2);
+#pragma unroll
+        for (int m = 0; m < MR; m++) {
+          if (m < M) {
+#pragma unroll
+            for (int q = 0; q < V; q += 4) {
+              const float4 a = *reinterpret_cast<const float4*>(arow[m] + k + q);
+              acc[m] = fmaf(a.x, wv[q], acc[m]); acc[m] = fmaf(a.y, wv[q + 1], acc[m]);
+              acc[m] = fmaf(a.z, wv[q + 2], acc[m]); acc[m] = fmaf(a.w, wv[q + 3], acc[m]);
+              if (DUAL) {
+                acc2[m] = fmaf(a.x, wv2[q], acc2[m]); acc2[m] = fmaf(a.y, wv2[q + 1], acc2[m]);
+                acc2[m] = fmaf(a.z, wv2[q + 2], acc2[m]); acc2[m] = fmaf(a.w, wv2[q + 3], acc2[m]);
+              }
+            }
+          }
+        }
+      }
+    } else {
+      for (int k = lane; k < P.K; k += 32) {
+        const float wv = to_f<WT>(w[k]);
+        const float wv2 = DUAL ? to_f<WT>(w2[k]) : 0.f;
+#pragma unroll
+        for (int m = 0; m < MR; m++) {
+          if (m < M) {
+            const float a = arow[m][k];
+            acc[m] = fmaf(a, wv, acc[m]);
+            if (DUAL) acc2[m] = fmaf(a, wv2, acc2[m]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+      if (m < M) {
+        const float v = warp_sum(acc[m]);
+        const float v2 = DUAL ? warp_sum(acc2[m]) : 0.f;
+        if (lane == 0) gemm_epilogue<WT, EPI>(P, P.C + coff + (size_t)crow_i[m] * P.ldc, crow_i[m], n, v, v2);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Depthwise causal convolution + SiLU over a chunk.  in: T rows (pitch ld_in) of `ch` channels; w [ch][taps] with the last tap
+// on the current token; `hist` [taps - 1][ch] holds the inputs of the taps - 1 tokens before the chunk (zeros at the start of a
+// sequence).  conv_history_update then replaces `hist` with the last taps - 1 inputs seen (it runs after the convolution).
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void causal_conv_silu(const float* __restrict__ in, int ld_in, const float* __restrict__ w, const float* __restrict__ b,
+                                 const float* __restrict__ hist, float* __restrict__ out, int ld_out, int T, int ch, int taps) {
+  const int t = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= ch) return;
+  float acc = b[c];
+  for (int k = 0; k < taps; k++) {
+    const int tau = t - (taps - 1) + k;
+    const float v = tau >= 0 ? in[(size_t)tau * ld_in + c] : hist[(size_t)(taps - 1 + tau) * ch + c];
+    acc = fmaf(w[(size_t)c * taps + k], v, acc);
+  }
+  out[(size_t)t * ld_out + c] = silu_f(acc);
+}
+__global__ void conv_history_update(const float* __restrict__ in, int ld_in, float* __restrict__ hist, int T, int ch, int taps) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= ch) return;
+  for (int j = 0; j < taps - 1; j++) {   // ascending: slot j is read (as slot T + j of the old history) before it is written
+    const int tau = T - (taps - 1) + j;
+    hist[(size_t)j * ch + c] = tau >= 0 ? in[(size_t)tau * ld_in + c] : hist[(size_t)(taps - 1 + tau) * ch + c];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// State-space-duality recurrence over a chunk, one CTA per (head, slice of PB value channels), sequential over the tokens.
+// Thread (pl, s) owns value channel p = p0 + pl and the state entries n = s, s + 8, ... (R of them) of S[h][p][:] in registers;
+// the eight threads of a channel reduce y with shuffles.  Inputs of 16 tokens at a time are staged in shared memory.
+//   dt = softplus(raw_dt + dt_bias_h);  S <- exp(-exp(A_log_h) dt) S + dt B x^T;  y = S^T C + D_h x;  out = y silu(z)
+// proj: the input projection's rows [z | . | . | . | raw dt]; xbc: the convolved [x | B | C] rows.  Head h reads B/C group h / (H / G).
+// ---------------------------------------------------------------------------------------------------------------------
+template <int R>
+__global__ void __launch_bounds__(512) ssd_scan(const float* __restrict__ proj, int ld_proj, int z_off, int dt_off,
+                                                const float* __restrict__ xbc, int ld_xbc, int x_off, int b_off, int c_off,
+                                                const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                                                const float* __restrict__ Dskip, float* __restrict__ state,
+                                                float* __restrict__ out, int ld_out, int T, int H, int P, int N, int G, int PB) {
+  constexpr int TB = 16;
+  extern __shared__ float sm[];
+  float* s_dt = sm;                 // [TB]
+  float* s_dA = s_dt + TB;          // [TB]
+  float* s_B = s_dA + TB;           // [TB][N]
+  float* s_C = s_B + TB * N;        // [TB][N]
+  float* s_x = s_C + TB * N;        // [TB][PB]
+  float* s_z = s_x + TB * PB;       // [TB][PB]
+  const int h = blockIdx.x, p0 = blockIdx.y * PB, g = h / (H / G);
+  const int tid = threadIdx.x, pl = tid >> 3, s = tid & 7, p = p0 + pl;
+  const bool pok = pl < PB && p < P;
+  float S[R];
+#pragma unroll
+  for (int r = 0; r < R; r++) {
+    const int n = s + 8 * r;
+    S[r] = (pok && n < N) ? state[((size_t)h * P + p) * N + n] : 0.f;
+  }
+  const float a = -expf(A_log[h]), dsk = Dskip[h], dtb = dt_bias[h];
+  for (int t0 = 0; t0 < T; t0 += TB) {
+    const int nt = min(TB, T - t0);
+    __syncthreads();
+    for (int i = tid; i < nt; i += blockDim.x) {
+      const float dt = softplus_f(proj[(size_t)(t0 + i) * ld_proj + dt_off + h] + dtb);
+      s_dt[i] = dt;
+      s_dA[i] = expf(a * dt);
+    }
+    for (int i = tid; i < nt * N; i += blockDim.x) {
+      const int tt = i / N, n = i - tt * N;
+      s_B[i] = xbc[(size_t)(t0 + tt) * ld_xbc + b_off + g * N + n];
+      s_C[i] = xbc[(size_t)(t0 + tt) * ld_xbc + c_off + g * N + n];
+    }
+    for (int i = tid; i < nt * PB; i += blockDim.x) {
+      const int tt = i / PB, q = i - tt * PB, pp = p0 + q;
+      s_x[i] = pp < P ? xbc[(size_t)(t0 + tt) * ld_xbc + x_off + h * P + pp] : 0.f;
+      s_z[i] = pp < P ? proj[(size_t)(t0 + tt) * ld_proj + z_off + h * P + pp] : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; tt++) {
+      const float dt = s_dt[tt], dA = s_dA[tt];
+      const float xv = pl < PB ? s_x[tt * PB + pl] : 0.f;
+      const float dx = dt * xv;
+      float y = 0.f;
+#pragma unroll
+      for (int r = 0; r < R; r++) {
+        const int n = s + 8 * r;
+        if (n < N) {
+          S[r] = fmaf(dA, S[r], dx * s_B[tt * N + n]);
+          y = fmaf(S[r], s_C[tt * N + n], y);
+        }
+      }
+      y += __shfl_xor_sync(0xffffffffu, y, 1);
+      y += __shfl_xor_sync(0xffffffffu, y, 2);
+      y += __shfl_xor_sync(0xffffffffu, y, 4);
+      if (s == 0 && pok) {
+        y = fmaf(dsk, xv, y);
+        out[(size_t)(t0 + tt) * ld_out + h * P + p] = y * silu_f(s_z[tt * PB + pl]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; r++) {
+    const int n = s + 8 * r;
+    if (pok && n < N) state[((size_t)h * P + p) * N + n] = S[r];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Sliding-window softmax attention over cached latents with the key up-projection absorbed into the query:
+//   score(i, j) = scale * qa[i][h] . c[j]   for  0 <= i - j < window,   o[i][h] = sum_j softmax_j(score) c[j]
+// qa [T][H][R] = per-head W_uk^T q; the caller then applies the per-head value up-projection to o [T][H][R].  The latent of
+// position j is row j % ring of `cache`.  A CTA of 8 warps takes TQ consecutive tokens x 8 / TQ heads (one warp each) and walks
+// the union of their windows in tiles of 32 keys staged in shared memory, so a tile is read once per CTA; lane = key for the
+// scores, lane = latent channel (mod 32) for the weighted sum.  Online softmax in fp32.
+// ---------------------------------------------------------------------------------------------------------------------
+template <typename CT, int RV>
+__global__ void __launch_bounds__(256) latent_swa_attn(const float* __restrict__ qa, const CT* __restrict__ cache, float* __restrict__ out,
+                                                       int T, int H, int R, const int* __restrict__ ctl, int window, int ring,
+                                                       float scale, int TQ) {
+  extern __shared__ float sm[];
+  const int NW = 8, HB = NW / TQ;
+  float* qs = sm;                 // [NW][R]
+  float* ks = sm + NW * R;        // [32][R + 1]
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int tq0 = blockIdx.x * TQ, t = tq0 + (w % TQ), h = blockIdx.y * HB + w / TQ;
+  const bool active = t < T && h < H;
+  const int pos0 = ctl[0];
+  for (int r = lane; r < R; r += 32) qs[w * R + r] = active ? qa[((size_t)t * H + h) * R + r] * scale : 0.f;
+  const int i = pos0 + t;
+  const int lo_w = max(0, i - window + 1), hi_w = i;
+  const int lo = max(0, pos0 + tq0 - window + 1), hi = pos0 + min(T, tq0 + TQ) - 1;
+  float m = -1e30f, l = 0.f, acc[RV];
+#pragma unroll
+  for (int k = 0; k < RV; k++) acc[k] = 0.f;
+  for (int j0 = lo; j0 <= hi; j0 += 32) {
+    __syncthreads();
+    for (int e = threadIdx.x; e < 32 * R; e += blockDim.x) {
+      const int jj = e / R, r = e - jj * R, j = j0 + jj;
+      ks[jj * (R + 1) + r] = j <= hi ? to_f<CT>(cache[(size_t)(j % ring) * R + r]) : 0.f;
+    }
+    __syncthreads();
+    const int j = j0 + lane;
+    const bool valid = active && j >= lo_w && j <= hi_w;
+    if (!__any_sync(0xffffffffu, valid)) continue;
+    float s = 0.f;
+    const float* kr = ks + lane * (R + 1);
+    const float* qr = qs + w * R;
+    for (int r = 0; r < R; r++) s = fmaf(qr[r], kr[r], s);
+    s = valid ? s : -1e30f;
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);
+    const float p = valid ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int k = 0; k < RV; k++) acc[k] *= corr;
+    for (int jj = 0; jj < 32; jj++) {
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      if (pj == 0.f) continue;
+      const float* c = ks + jj * (R + 1);
+#pragma unroll
+      for (int k = 0; k < RV; k++) {
+        const int r = lane + 32 * k;
+        if (r < R) acc[k] = fmaf(pj, c[r], acc[k]);
+      }
+    }
+    m = m_new;
+  }
+  if (active) {
+    const float inv = 1.f / l;
+#pragma unroll
+    for (int k = 0; k < RV; k++) {
+      const int r = lane + 32 * k;
+      if (r < R) out[((size_t)t * H + h) * R + r] = acc[k] * inv;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Router of a routed feed-forward, one CTA per token.  s = sigmoid(logits); the `top` experts with the largest s + correction
+// are taken (ties: lower index first), slot = rank; weights = s / (sum of the chosen s + 1e-20) * scale.
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void moe_route(const float* __restrict__ logits, const float* __restrict__ correction, int E, int top, float scale,
+                          int* __restrict__ idx, float* __restrict__ wgt) {
+  extern __shared__ float sm[];
+  float* sc = sm;            // [E]
+  float* ch = sm + E;        // [E]
+  float* sel = ch + E;       // [top]
+  const int t = blockIdx.x;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const float s = sigmoid_f(logits[(size_t)t * E + e]);
+    sc[e] = s;
+    ch[e] = s + (correction ? correction[e] : 0.f);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const float c = ch[e];
+    int rank = 0;
+    for (int i = 0; i < E; i++) rank += (ch[i] > c || (ch[i] == c && i < e)) ? 1 : 0;
+    if (rank < top) { idx[(size_t)t * top + rank] = e; sel[rank] = sc[e]; }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float sum = 0.f;
+    for (int k = 0; k < top; k++) sum += sel[k];
+    const float inv = scale / (sum + 1e-20f);
+    for (int k = 0; k < top; k++) wgt[(size_t)t * top + k] = sel[k] * inv;
+  }
+}
+
+// Groups the `pairs` (token, slot) pairs of a chunk by expert: perm lists the pairs expert by expert (stable), tiles cuts every
+// expert's run into row tiles of at most `bm` rows {expert, first index into perm, rows}.  One CTA.
+__global__ void __launch_bounds__(256) moe_plan(const int* __restrict__ idx, int pairs, int E, int bm, int* __restrict__ perm,
+                                                int4* __restrict__ tiles, int* __restrict__ n_tiles) {
+  extern __shared__ int smi[];
+  int* cnt = smi;            // [E]
+  int* off = smi + E;        // [E]
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int c = 0;
+    for (int i = 0; i < pairs; i++) c += idx[i] == e ? 1 : 0;
+    cnt[e] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, nt = 0;
+    for (int e = 0; e < E; e++) {
+      off[e] = o;
+      for (int r = 0; r < cnt[e]; r += bm) tiles[nt++] = make_int4(e, o + r, min(bm, cnt[e] - r), 0);
+      o += cnt[e];
+    }
+    *n_tiles = nt;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int o = off[e];
+    for (int i = 0; i < pairs; i++) if (idx[i] == e) perm[o++] = i;
+  }
+}
+
+__global__ void moe_combine(float* __restrict__ x, int ldx, const float* __restrict__ y, const float* __restrict__ wgt, int top,
+                            int width, float alpha) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < top; k++) s = fmaf(wgt[(size_t)t * top + k], y[((size_t)t * top + k) * width + c], s);
+    x[(size_t)t * ldx + c] += alpha * s;
+  }
+}
+
+// arg-max of one logits row -> Ctrl::argmax_key (lowest index on ties), optionally feeding the next token of a device-side
+// greedy loop: tok_out[0] = arg-max, log[step] = arg-max.
+__global__ void __launch_bounds__(1024) argmax_row(const float* __restrict__ logits, int vocab, Ctrl* __restrict__ ctrl, int* tok_out,
+                                                   int* log, int step) {
+  __shared__ unsigned long long best[32];
+  unsigned long long b = 0ull;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const unsigned long long key = ((unsigned long long)orderable(logits[i]) << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)i);
+    if (key > b) b = key;
+  }
+  for (int o = 16; o; o >>= 1) { const unsigned long long v = __shfl_xor_sync(0xffffffffu, b, o); if (v > b) b = v; }
+  if ((threadIdx.x & 31) == 0) best[threadIdx.x >> 5] = b;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); w++) if (best[w] > b) b = best[w];
+    ctrl->argmax_key = b;
+    const int tok = (int)(0xFFFFFFFFu - (unsigned)(b & 0xFFFFFFFFull));
+    if (tok_out) tok_out[0] = tok;
+    if (log) log[step] = tok;
+  }
+}
+
+// device-side greedy loop: the token of the last arg-max becomes the next chunk's only token and is logged
+__global__ void greedy_feed(const Ctrl* __restrict__ ctrl, int* __restrict__ tok, int* __restrict__ log, int* __restrict__ step) {
+  const int t = (int)(0xFFFFFFFFu - (unsigned)(ctrl->argmax_key & 0xFFFFFFFFull));
+  tok[0] = t;
+  log[*step] = t;
+  *step += 1;
+}
+
+}  // namespace hy
+}  // namespace dsk

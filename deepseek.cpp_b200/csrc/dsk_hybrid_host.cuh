@@ -1,0 +1,692 @@
+// dsk_hybrid_host.cuh — host side of the layer-list ("hybrid") model family inside libdsk: model description, tensor upload by
+// name, the per-sequence state (recurrent states, convolution histories, latent ring caches) and the chunk step that
+// dsk_forward / dsk_forward_chunk / dsk_decode_greedy drive.  Included at the end of dsk_engine.cu (it uses that file's error,
+// allocation and sampling helpers); dsk_model::hy / dsk_state::hy point at the structures below.
+//
+// Tensor names (safetensors, [out, in] matrices):  embed, side.embed, final.norm, and per layer i ("l<i>."):
+//   norm1 | mix.in, mix.conv, mix.conv.b, mix.dt_bias, mix.A_log, mix.D, mix.norm, mix.o              (state-space mixer)
+//         | mix.q, mix.dkv, mix.dkv.norm, mix.uk, mix.uv, mix.o                                        (latent attention)
+//   mlp.router, mlp.correction, mlp.e<j>.gate|up|down                                                 (routed feed-forward)
+//   side.gate, side.proj, side.norm                                                                   (per-layer token input)
+// A layer computes, with h = norm1(x):  x += m (mixer(h) + ff(h));  then, when the model has a per-layer token table,
+// g = gelu_tanh(side.gate x) * side.embed[token][i*sd : (i+1)*sd],  y = side.proj g,  x += m * rmsnorm(y) * side.norm.
+#pragma once
+
+namespace hyb {
+using namespace dsk;
+using namespace dsk::hy;
+
+struct HTensor {
+  void* p = nullptr;       // model quant type (float | bf16)
+  long long rows = 0, cols = 0;
+  bool present = false;
+};
+
+struct HLayer {
+  dsk_layer_spec sp;
+  float* norm1 = nullptr;
+  // state-space mixer
+  HTensor in, o;
+  float *conv_w = nullptr, *conv_b = nullptr, *dt_bias = nullptr, *A_log = nullptr, *D = nullptr, *mnorm = nullptr;
+  // latent attention
+  HTensor q, dkv, ukT, uv;          // ukT: [heads][kv_rank][dim], the transposed key up-projection (absorbed into the query)
+  float* dkv_norm = nullptr;
+  int owner = -1;                   // layer whose latent cache this layer reads (itself unless kv_from)
+  int ring = 0;                     // rows of this layer's own ring cache (owners only)
+  // routed feed-forward
+  HTensor gate_s, up_s, down_s;     // expert stacks [E][ff][width], [E][ff][width], [E][width][ff]
+  std::vector<char> have;           // 3 E flags
+  float *router = nullptr, *correction = nullptr;
+  // per-layer token input
+  HTensor sgate, sproj;
+  float* snorm = nullptr;
+};
+
+struct Model {
+  dsk_hybrid_config c;
+  std::vector<HLayer> L;
+  HTensor embed, side_embed;
+  float* final_norm = nullptr;
+  size_t wsize = 4;                 // bytes per matrix element
+};
+
+struct LayerState {
+  float* ssm = nullptr;             // [heads][vdim][state]
+  float* hist = nullptr;            // [conv - 1][channels]
+  void* cache = nullptr;            // [ring][kv_rank] (owner layers)
+  size_t ssm_bytes = 0, hist_bytes = 0, cache_bytes = 0;
+};
+
+struct State {
+  std::vector<LayerState> L;
+  int chunk = 0;
+  int next_pos = 0;
+  int *d_tok = nullptr, *d_want = nullptr, *d_ctl = nullptr, *d_idx = nullptr, *d_perm = nullptr, *d_ntiles = nullptr;
+  int4* d_tiles = nullptr;
+  int max_tiles = 0;
+  float *x = nullptr, *h = nullptr, *b0 = nullptr, *b1 = nullptr, *b2 = nullptr, *b3 = nullptr, *wgt = nullptr, *logits = nullptr;
+  int *h_tok = nullptr, *h_want = nullptr;   // pinned staging of a chunk's token ids / wanted rows
+  std::vector<void*> allocs;
+  cudaGraphExec_t step_graph = nullptr;      // captured greedy decode step (arg-max -> token -> one-token chunk)
+  long long launches = 0;
+};
+
+static bool is_ssd(const dsk_layer_spec& s) { return s.mixer == DSK_MIX_SSD; }
+static long long ssd_inner(const dsk_layer_spec& s) { return (long long)s.ssm_heads * s.ssm_vdim; }
+static long long ssd_channels(const dsk_layer_spec& s) { return ssd_inner(s) + 2LL * s.ssm_groups * s.ssm_state; }
+static long long ssd_proj(const dsk_layer_spec& s) { return ssd_inner(s) + ssd_channels(s) + s.ssm_heads; }
+
+static int validate(const dsk_hybrid_config& c, const dsk_layer_spec* L) {
+  if (c.dim <= 0 || c.vocab_size <= 0 || c.n_layers <= 0 || c.max_seq_len <= 0) return fail(-1, "hybrid model: bad dimensions");
+  if (c.quant != DSK_F32 && c.quant != DSK_BF16) return fail(-1, "hybrid models run with quant fp32 or bf16");
+  if (c.norm_groups <= 0 || c.dim % c.norm_groups != 0) return fail(-1, "norm groups %d do not divide width %d", c.norm_groups, c.dim);
+  if (c.chunk < 1 || c.chunk > 4096) return fail(-1, "chunk %d out of range (1..4096)", c.chunk);
+  if (c.side_dim < 0) return fail(-1, "negative side_dim");
+  for (int i = 0; i < c.n_layers; i++) {
+    const dsk_layer_spec& s = L[i];
+    if (s.mixer == DSK_MIX_SSD) {
+      if (s.ssm_heads <= 0 || s.ssm_vdim <= 0 || s.ssm_state <= 0 || s.ssm_groups <= 0 || s.ssm_conv < 1 || s.ssm_norm_groups <= 0)
+        return fail(-1, "layer %d: bad state-space mixer sizes", i);
+      if (s.ssm_heads % s.ssm_groups != 0) return fail(-1, "layer %d: heads %d not a multiple of groups %d", i, s.ssm_heads, s.ssm_groups);
+      if ((s.ssm_heads * s.ssm_vdim) % s.ssm_norm_groups != 0) return fail(-1, "layer %d: norm_groups does not divide the inner width", i);
+      if (s.ssm_state > 256) return fail(-1, "layer %d: state size %d > 256 unsupported (the scan keeps the state in registers)", i, s.ssm_state);
+    } else if (s.mixer == DSK_MIX_LATENT_SWA) {
+      if (s.att_heads <= 0 || s.att_dim <= 0 || s.att_vdim <= 0 || s.att_kv_rank <= 0 || s.att_window <= 0)
+        return fail(-1, "layer %d: bad latent-attention sizes", i);
+      if (s.att_kv_rank > 1024) return fail(-1, "layer %d: kv_rank %d > 1024 unsupported", i, s.att_kv_rank);
+      if (s.att_kv_from >= 0) {
+        const int j = s.att_kv_from;
+        if (j >= i || L[j].mixer != DSK_MIX_LATENT_SWA || L[j].att_kv_from >= 0 || L[j].att_kv_rank != s.att_kv_rank)
+          return fail(-1, "layer %d: kv_from %d must name an earlier latent-attention layer that projects its own latent of the same rank", i, j);
+      }
+    } else return fail(-1, "layer %d: unknown mixer %d", i, s.mixer);
+    if (s.ff_kind == DSK_FF_MOE) {
+      if (s.ff_experts <= 0 || s.ff_top <= 0 || s.ff_top > s.ff_experts || s.ff_hidden <= 0) return fail(-1, "layer %d: bad routed feed-forward sizes", i);
+      if (s.ff_experts > 4096) return fail(-1, "layer %d: more than 4096 experts unsupported", i);
+    } else if (s.ff_kind != DSK_FF_NONE) return fail(-1, "layer %d: unknown feed-forward kind %d", i, s.ff_kind);
+  }
+  return 0;
+}
+
+static void set_kernel_attrs() {
+  static bool done = false;
+  if (done) return;
+  const int big = 200 * 1024;
+  cudaFuncSetAttribute(latent_swa_attn<float, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(latent_swa_attn<float, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(latent_swa_attn<float, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(latent_swa_attn<float, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  done = true;
+}
+
+static dsk_model* model_create(const dsk_hybrid_config* cfg, const dsk_layer_spec* layers, int rank, int n_ranks) {
+  if (need_device()) return nullptr;
+  if (!cfg || !layers) { fail(-1, "bad arguments"); return nullptr; }
+  if (n_ranks != 1 || rank != 0) { fail(-1, "hybrid models run on one GPU (n_ranks must be 1)"); return nullptr; }
+  if (validate(*cfg, layers)) return nullptr;
+  set_kernel_attrs();
+  dsk_model* m = new dsk_model();
+  Model* M = new Model();
+  m->hy = M;
+  M->c = *cfg;
+  M->wsize = cfg->quant == DSK_BF16 ? 2 : 4;
+  m->c = dsk_config{};
+  m->c.dim = cfg->dim; m->c.vocab_size = cfg->vocab_size; m->c.n_layers = cfg->n_layers; m->c.max_seq_len = cfg->max_seq_len;
+  m->c.quant = cfg->quant; m->c.norm_eps = cfg->norm_eps;
+  M->L.resize(cfg->n_layers);
+  for (int i = 0; i < cfg->n_layers; i++) {
+    HLayer& L = M->L[i];
+    L.sp = layers[i];
+    if (L.sp.ff_kind == DSK_FF_MOE) L.have.assign(3 * (size_t)L.sp.ff_experts, 0);
+    if (L.sp.mixer == DSK_MIX_LATENT_SWA) L.owner = L.sp.att_kv_from >= 0 ? L.sp.att_kv_from : i;
+  }
+  // ring caches: the owner keeps the widest window among its readers plus one chunk, capped by the sequence limit
+  for (int i = 0; i < cfg->n_layers; i++) {
+    const HLayer& L = M->L[i];
+    if (L.sp.mixer != DSK_MIX_LATENT_SWA) continue;
+    HLayer& O = M->L[L.owner];
+    const long long need = (long long)L.sp.att_window - 1 + cfg->chunk;
+    O.ring = (int)std::max<long long>(O.ring, std::min<long long>(need, (long long)cfg->max_seq_len));
+  }
+  return m;
+}
+
+static void model_free(dsk_model* m) { delete m->hy; m->hy = nullptr; }
+
+template <typename ST>
+static void launch_convert(const void* src, void* dst, long long rows, long long cols, int tr, bool to_bf16) {
+  const long long n = rows * cols;
+  const unsigned grid = (unsigned)std::max<long long>(1, std::min<long long>((n + 255) / 256, 1 << 16));
+  if (to_bf16) convert_kernel<ST, __nv_bfloat16><<<grid, 256>>>((const ST*)src, (__nv_bfloat16*)dst, rows, cols, tr);
+  else convert_kernel<ST, float><<<grid, 256>>>((const ST*)src, (float*)dst, rows, cols, tr);
+}
+
+// payload (BF16 or F32; host or device) of logical shape rows x cols (cols == 0: a vector) -> dst (fp32 or bf16), optionally
+// transposed per head (tr)
+static int put(const char* name, int dtype, const int64_t shape[4], const void* data, size_t nbytes, int on_dev, long long rows,
+               long long cols, void* dst, bool to_bf16, int tr) {
+  if (dtype != DSK_DT_BF16 && dtype != DSK_DT_F32) return fail(-4, "tensor %s: dtype %s unsupported (BF16 or F32)", name, dtype_name(dtype));
+  const size_t es = dtype == DSK_DT_BF16 ? 2 : 4;
+  const long long n = rows * std::max<long long>(cols, 1);
+  if (shape[0] != rows || shape[1] != cols || shape[2] != 0 || nbytes != (size_t)n * es)
+    return fail(-4, "tensor mismatch for %s: expected shape=[%lld,%lld], got shape=[%lld,%lld,%lld] (%zu bytes)", name, rows, cols,
+                (long long)shape[0], (long long)shape[1], (long long)shape[2], nbytes);
+  const void* src = data;
+  void* staging = nullptr;
+  if (!on_dev) {
+    CK(cudaMalloc(&staging, nbytes ? nbytes : 16));
+    CK(cudaMemcpy(staging, data, nbytes, cudaMemcpyHostToDevice));
+    src = staging;
+  }
+  if (dtype == DSK_DT_BF16) launch_convert<__nv_bfloat16>(src, dst, rows, std::max<long long>(cols, 1), tr, to_bf16);
+  else launch_convert<float>(src, dst, rows, std::max<long long>(cols, 1), tr, to_bf16);
+  CK(cudaGetLastError());
+  if (staging) { CK(cudaDeviceSynchronize()); CK(cudaFree(staging)); }
+  return 0;
+}
+
+static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape[4], const void* data, size_t nbytes, int on_dev) {
+  Model* M = m->hy;
+  const dsk_hybrid_config& c = M->c;
+  const bool bf = c.quant == DSK_BF16;
+  const std::string nm(name);
+  // matrix in the model's quant type
+  auto MAT = [&](HTensor& t, long long rows, long long cols, int tr = 0) -> int {
+    if (t.present) return fail(-4, "tensor %s uploaded twice", name);
+    if (dmalloc(m, &t.p, (size_t)rows * cols * M->wsize + 16)) return -2;
+    t.rows = rows; t.cols = cols; t.present = true;
+    return put(name, dtype, shape, data, nbytes, on_dev, rows, cols, t.p, bf, tr);
+  };
+  // fp32 side tensor (norm weights, biases, decays, router)
+  auto F32 = [&](float** dst, long long rows, long long cols) -> int {
+    if (*dst) return fail(-4, "tensor %s uploaded twice", name);
+    if (dmalloc(m, (void**)dst, (size_t)rows * std::max<long long>(cols, 1) * 4)) return -2;
+    return put(name, dtype, shape, data, nbytes, on_dev, rows, cols, *dst, false, 0);
+  };
+  if (nm == "embed") return MAT(M->embed, c.vocab_size, c.dim);
+  if (nm == "final.norm") return F32(&M->final_norm, c.dim, 0);
+  if (nm == "side.embed") {
+    if (c.side_dim <= 0) return fail(-4, "tensor %s: the model has no per-layer token input", name);
+    return MAT(M->side_embed, c.vocab_size, (long long)c.side_dim * c.n_layers);
+  }
+  if (nm.size() < 3 || nm[0] != 'l') return fail(-4, "unknown tensor name %s", name);
+  char* end = nullptr;
+  const long li = strtol(name + 1, &end, 10);
+  if (end == name + 1 || *end != '.' || li < 0 || li >= c.n_layers) return fail(-4, "unknown tensor name %s", name);
+  HLayer& L = M->L[li];
+  const dsk_layer_spec& s = L.sp;
+  const std::string rest(end + 1);
+  if (rest == "norm1") return F32(&L.norm1, c.dim, 0);
+  if (rest.rfind("mix.", 0) == 0) {
+    const std::string k = rest.substr(4);
+    if (is_ssd(s)) {
+      const long long inner = ssd_inner(s), ch = ssd_channels(s);
+      if (k == "in") return MAT(L.in, ssd_proj(s), c.dim);
+      if (k == "conv") return F32(&L.conv_w, ch, s.ssm_conv);
+      if (k == "conv.b") return F32(&L.conv_b, ch, 0);
+      if (k == "dt_bias") return F32(&L.dt_bias, s.ssm_heads, 0);
+      if (k == "A_log") return F32(&L.A_log, s.ssm_heads, 0);
+      if (k == "D") return F32(&L.D, s.ssm_heads, 0);
+      if (k == "norm") return F32(&L.mnorm, inner, 0);
+      if (k == "o") return MAT(L.o, c.dim, inner);
+    } else {
+      const long long H = s.att_heads;
+      if (k == "q") return MAT(L.q, H * s.att_dim, c.dim);
+      if (k == "uk") return MAT(L.ukT, H * s.att_dim, s.att_kv_rank, s.att_dim);
+      if (k == "uv") return MAT(L.uv, H * s.att_vdim, s.att_kv_rank);
+      if (k == "o") return MAT(L.o, c.dim, H * s.att_vdim);
+      if (s.att_kv_from < 0) {
+        if (k == "dkv") return MAT(L.dkv, s.att_kv_rank, c.dim);
+        if (k == "dkv.norm") return F32(&L.dkv_norm, s.att_kv_rank, 0);
+      }
+    }
+    return fail(-4, "unknown tensor name %s for this layer's mixer", name);
+  }
+  if (rest.rfind("mlp.", 0) == 0 && s.ff_kind == DSK_FF_MOE) {
+    const std::string k = rest.substr(4);
+    const long long E = s.ff_experts, ff = s.ff_hidden;
+    if (k == "router") return F32(&L.router, E, c.dim);
+    if (k == "correction") return F32(&L.correction, E, 0);
+    if (k.size() > 1 && k[0] == 'e') {
+      char* e2 = nullptr;
+      const long e = strtol(k.c_str() + 1, &e2, 10);
+      if (e2 != k.c_str() + 1 && *e2 == '.' && e >= 0 && e < E) {
+        const std::string part(e2 + 1);
+        const int which = part == "gate" ? 0 : part == "up" ? 1 : part == "down" ? 2 : -1;
+        if (which >= 0) {
+          HTensor& st = which == 0 ? L.gate_s : which == 1 ? L.up_s : L.down_s;
+          if (!st.p) {
+            if (dmalloc(m, &st.p, (size_t)E * ff * c.dim * M->wsize + 16)) return -2;
+            st.rows = which == 2 ? c.dim : ff; st.cols = which == 2 ? ff : c.dim;
+          }
+          if (L.have[(size_t)which * E + e]) return fail(-4, "tensor %s uploaded twice", name);
+          L.have[(size_t)which * E + e] = 1;
+          return put(name, dtype, shape, data, nbytes, on_dev, st.rows, st.cols, (char*)st.p + (size_t)e * ff * c.dim * M->wsize, bf, 0);
+        }
+      }
+    }
+    return fail(-4, "unknown tensor name %s", name);
+  }
+  if (rest.rfind("side.", 0) == 0 && c.side_dim > 0) {
+    const std::string k = rest.substr(5);
+    if (k == "gate") return MAT(L.sgate, c.side_dim, c.dim);
+    if (k == "proj") return MAT(L.sproj, c.dim, c.side_dim);
+    if (k == "norm") return F32(&L.snorm, c.dim, 0);
+  }
+  return fail(-4, "unknown tensor name %s", name);
+}
+
+static int finalize(dsk_model* m) {
+  Model* M = m->hy;
+  const dsk_hybrid_config& c = M->c;
+  if (!M->embed.present) return fail(-5, "missing tensor embed");
+  if (!M->final_norm) return fail(-5, "missing tensor final.norm");
+  if (c.side_dim > 0 && !M->side_embed.present) return fail(-5, "missing tensor side.embed");
+  for (int i = 0; i < c.n_layers; i++) {
+    HLayer& L = M->L[i];
+    const dsk_layer_spec& s = L.sp;
+    if (!L.norm1) return fail(-5, "missing tensor l%d.norm1", i);
+    if (is_ssd(s)) {
+      if (!L.in.present || !L.o.present || !L.conv_w || !L.conv_b || !L.dt_bias || !L.A_log || !L.D || !L.mnorm)
+        return fail(-5, "layer %d: missing state-space mixer tensors (mix.in, conv, conv.b, dt_bias, A_log, D, norm, o)", i);
+    } else {
+      if (!L.q.present || !L.ukT.present || !L.uv.present || !L.o.present) return fail(-5, "layer %d: missing latent-attention tensors (mix.q, uk, uv, o)", i);
+      if (s.att_kv_from < 0 && (!L.dkv.present || !L.dkv_norm)) return fail(-5, "layer %d: missing mix.dkv / mix.dkv.norm", i);
+    }
+    if (s.ff_kind == DSK_FF_MOE) {
+      if (!L.router || !L.correction) return fail(-5, "layer %d: missing mlp.router / mlp.correction", i);
+      for (size_t k = 0; k < L.have.size(); k++)
+        if (!L.have[k]) return fail(-5, "layer %d: missing expert tensor mlp.e%zu.%s", i, k % s.ff_experts, k / s.ff_experts == 0 ? "gate" : k / s.ff_experts == 1 ? "up" : "down");
+    }
+    if (c.side_dim > 0 && (!L.sgate.present || !L.sproj.present || !L.snorm)) return fail(-5, "layer %d: missing side.gate / side.proj / side.norm", i);
+  }
+  CK(cudaDeviceSynchronize());
+  return 0;
+}
+
+// algorithmic weight bytes one decoded token streams
+static double active_bytes(const dsk_model* m) {
+  const Model* M = m->hy;
+  const dsk_hybrid_config& c = M->c;
+  const double ws = (double)M->wsize, W = c.dim;
+  double tot = W * ws + (double)c.vocab_size * W * ws + W * 4;
+  for (const HLayer& L : M->L) {
+    const dsk_layer_spec& s = L.sp;
+    double mat = 0, f32 = W;
+    if (is_ssd(s)) { mat += (double)ssd_proj(s) * W + W * ssd_inner(s); f32 += (double)ssd_channels(s) * (s.ssm_conv + 1) + 3.0 * s.ssm_heads + ssd_inner(s); }
+    else {
+      mat += (double)s.att_heads * s.att_dim * W + (double)s.att_heads * (s.att_dim + s.att_vdim) * s.att_kv_rank + W * s.att_heads * s.att_vdim;
+      if (s.att_kv_from < 0) { mat += (double)s.att_kv_rank * W; f32 += s.att_kv_rank; }
+    }
+    if (s.ff_kind == DSK_FF_MOE) { mat += 3.0 * s.ff_top * s.ff_hidden * W; f32 += (double)s.ff_experts * (W + 1); }
+    if (c.side_dim > 0) { mat += 2.0 * c.side_dim * W + c.side_dim; f32 += W; }
+    tot += mat * ws + f32 * 4;
+  }
+  return tot;
+}
+
+// kernels one decoded token launches (embedding + layers + final norm + LM head + arg-max)
+static int launches_per_token(const dsk_model* m) {
+  const Model* M = m->hy;
+  int n = 4;
+  for (const HLayer& L : M->L) {
+    const dsk_layer_spec& s = L.sp;
+    n += 1 + (is_ssd(s) ? 5 + (s.ssm_conv > 1 ? 1 : 0) : 5 + (s.att_kv_from < 0 ? 2 : 0));
+    if (s.ff_kind == DSK_FF_MOE) n += 5;
+    if (M->c.side_dim > 0) n += 3;
+  }
+  return n;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// state
+// ---------------------------------------------------------------------------------------------------------------------
+static int salloc(State* S, void** p, size_t bytes) {
+  CK(cudaMalloc(p, bytes ? bytes : 16));
+  CK(cudaMemset(*p, 0, bytes ? bytes : 16));
+  S->allocs.push_back(*p);
+  return 0;
+}
+
+static int state_reset(dsk_state* s) {
+  State* S = s->hy;
+  for (LayerState& l : S->L) {
+    if (l.ssm) CK(cudaMemsetAsync(l.ssm, 0, l.ssm_bytes, s->stream));
+    if (l.hist) CK(cudaMemsetAsync(l.hist, 0, l.hist_bytes, s->stream));
+    if (l.cache) CK(cudaMemsetAsync(l.cache, 0, l.cache_bytes, s->stream));
+  }
+  S->next_pos = 0;
+  s->last_pos = -1;
+  s->have_logits = false;
+  return 0;
+}
+
+static dsk_state* state_create(dsk_model* m) {
+  Model* M = m->hy;
+  const dsk_hybrid_config& c = M->c;
+  dsk_state* s = new dsk_state();
+  State* S = new State();
+  s->m = m;
+  s->hy = S;
+  S->chunk = c.chunk;
+  const size_t Tc = c.chunk;
+  // the pieces the shared sampling / arg-max code reads
+  cudaMalloc((void**)&s->ctrl, sizeof(Ctrl)); cudaMemset(s->ctrl, 0, sizeof(Ctrl));
+  cudaMallocHost((void**)&s->h_ctrl, sizeof(Ctrl)); memset(s->h_ctrl, 0, sizeof(Ctrl));
+  s->token_log_cap = 1 << 16;
+  cudaMalloc((void**)&s->token_log, s->token_log_cap * sizeof(int));
+  cudaMalloc((void**)&s->step, sizeof(int));
+  cudaMalloc((void**)&s->sample_out, 4 * sizeof(float)); cudaMemset(s->sample_out, 0, 4 * sizeof(float));
+  cudaMalloc((void**)&s->logits, (size_t)c.vocab_size * 4); cudaMemset(s->logits, 0, (size_t)c.vocab_size * 4);
+  s->logits_src = s->logits;
+  cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking);
+  cudaEventCreate(&s->ev0); cudaEventCreate(&s->ev1);
+  if (cudaGetLastError() != cudaSuccess) { fail(-2, "state allocation failed"); return nullptr; }
+  size_t mx0 = c.dim, mx1 = c.dim, mx2 = c.dim, mx3 = c.dim, mxE = 1, mxTop = 1;
+  S->L.resize(c.n_layers);
+  for (int i = 0; i < c.n_layers; i++) {
+    const HLayer& L = M->L[i];
+    const dsk_layer_spec& sp = L.sp;
+    LayerState& ls = S->L[i];
+    if (is_ssd(sp)) {
+      ls.ssm_bytes = (size_t)sp.ssm_heads * sp.ssm_vdim * sp.ssm_state * 4;
+      ls.hist_bytes = (size_t)std::max(1, sp.ssm_conv - 1) * ssd_channels(sp) * 4;
+      if (salloc(S, (void**)&ls.ssm, ls.ssm_bytes) || salloc(S, (void**)&ls.hist, ls.hist_bytes)) return nullptr;
+      mx0 = std::max<size_t>(mx0, ssd_proj(sp)); mx1 = std::max<size_t>(mx1, ssd_channels(sp));
+      mx2 = std::max<size_t>(mx2, ssd_inner(sp)); mx3 = std::max<size_t>(mx3, ssd_inner(sp));
+    } else {
+      if (L.owner == i) {
+        ls.cache_bytes = (size_t)L.ring * sp.att_kv_rank * 4;
+        if (salloc(S, &ls.cache, ls.cache_bytes)) return nullptr;
+      }
+      mx0 = std::max<size_t>(mx0, std::max((size_t)sp.att_heads * sp.att_dim, (size_t)sp.att_heads * sp.att_vdim));
+      mx1 = std::max<size_t>(mx1, sp.att_kv_rank);
+      mx2 = std::max<size_t>(mx2, (size_t)sp.att_heads * sp.att_kv_rank); mx3 = std::max<size_t>(mx3, (size_t)sp.att_heads * sp.att_kv_rank);
+    }
+    if (sp.ff_kind == DSK_FF_MOE) {
+      mxE = std::max<size_t>(mxE, sp.ff_experts); mxTop = std::max<size_t>(mxTop, sp.ff_top);
+      mx0 = std::max<size_t>(mx0, sp.ff_experts);
+      mx2 = std::max<size_t>(mx2, (size_t)sp.ff_top * sp.ff_hidden); mx3 = std::max<size_t>(mx3, (size_t)sp.ff_top * c.dim);
+    }
+    mx1 = std::max<size_t>(mx1, c.side_dim);
+  }
+  S->max_tiles = (int)(Tc * mxTop / 64 + mxE + 1);
+  int rc = 0;
+  rc |= salloc(S, (void**)&S->x, Tc * c.dim * 4) | salloc(S, (void**)&S->h, Tc * c.dim * 4);
+  rc |= salloc(S, (void**)&S->b0, Tc * mx0 * 4) | salloc(S, (void**)&S->b1, Tc * mx1 * 4) | salloc(S, (void**)&S->b2, Tc * mx2 * 4) | salloc(S, (void**)&S->b3, Tc * mx3 * 4);
+  rc |= salloc(S, (void**)&S->wgt, Tc * mxTop * 4) | salloc(S, (void**)&S->d_idx, Tc * mxTop * 4) | salloc(S, (void**)&S->d_perm, Tc * mxTop * 4);
+  rc |= salloc(S, (void**)&S->d_tiles, (size_t)S->max_tiles * sizeof(int4)) | salloc(S, (void**)&S->d_ntiles, 16);
+  rc |= salloc(S, (void**)&S->d_tok, Tc * 4) | salloc(S, (void**)&S->d_want, Tc * 4) | salloc(S, (void**)&S->d_ctl, 16);
+  rc |= salloc(S, (void**)&S->logits, Tc * (size_t)c.vocab_size * 4);
+  if (rc) { fail(-2, "state allocation failed"); return nullptr; }
+  if (cudaMallocHost((void**)&S->h_tok, Tc * 4) != cudaSuccess || cudaMallocHost((void**)&S->h_want, Tc * 4) != cudaSuccess) { fail(-2, "pinned allocation failed"); return nullptr; }
+  m->n_states++;
+  return s;
+}
+
+static void state_free(dsk_state* s) {
+  State* S = s->hy;
+  if (!S) return;
+  if (S->step_graph) cudaGraphExecDestroy(S->step_graph);
+  for (void* p : S->allocs) cudaFree(p);
+  cudaFreeHost(S->h_tok); cudaFreeHost(S->h_want);
+  delete S;
+  s->hy = nullptr;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// the chunk step
+// ---------------------------------------------------------------------------------------------------------------------
+static GemmP gp(const float* A, int lda, const void* W, int ldw, float* C, int ldc, int M, int N, int K) {
+  GemmP P{};
+  P.A = A; P.lda = lda; P.W = W; P.ldw = ldw; P.C = C; P.ldc = ldc; P.M = M; P.N = N; P.K = K;
+  P.a_div = 1; P.z_adiv = 1; P.alpha = 1.f;
+  return P;
+}
+
+template <typename WT>
+static void launch_gemm_t(int epi, const GemmP& P, int Z, bool small, int tile_cap, cudaStream_t st) {
+  if (small) {
+    const dim3 grid((unsigned)std::max(1, std::min((P.N + 7) / 8, 148 * 8)), (unsigned)Z);
+    switch (epi) {
+      case HEPI_STORE: gemv_rows<WT, HEPI_STORE><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_ADD: gemv_rows<WT, HEPI_ADD><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_GLU: gemv_rows<WT, HEPI_GLU><<<grid, 256, 0, st>>>(P); break;
+      default: gemv_rows<WT, HEPI_GELU_MUL><<<grid, 256, 0, st>>>(P); break;
+    }
+  } else {
+    const dim3 grid((unsigned)((P.N + 63) / 64), (unsigned)(P.tiles ? tile_cap : (P.M + 63) / 64), (unsigned)Z);
+    switch (epi) {
+      case HEPI_STORE: gemm_tiled<WT, HEPI_STORE><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_ADD: gemm_tiled<WT, HEPI_ADD><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_GLU: gemm_tiled<WT, HEPI_GLU><<<grid, 256, 0, st>>>(P); break;
+      default: gemm_tiled<WT, HEPI_GELU_MUL><<<grid, 256, 0, st>>>(P); break;
+    }
+  }
+}
+// C = A W^T (+ epilogue).  Z > 1: per-head batches or (gemv) one batch per routed (token, slot) pair.
+static void linear(State* S, bool bf16, int epi, const GemmP& P, int Z, cudaStream_t st, int tile_cap = 0) {
+  const bool small = P.z_expert != nullptr || (!P.tiles && P.M <= 4);
+  if (bf16) launch_gemm_t<__nv_bfloat16>(epi, P, Z, small, tile_cap, st);
+  else launch_gemm_t<float>(epi, P, Z, small, tile_cap, st);
+  S->launches++;
+}
+
+static void launch_scan(const dsk_layer_spec& sp, const float* proj, int ld_proj, const float* xbc, int ld_xbc, const HLayer& L,
+                        float* state, float* out, int T, cudaStream_t st) {
+  const int H = sp.ssm_heads, P = sp.ssm_vdim, N = sp.ssm_state, G = sp.ssm_groups;
+  const int inner = H * P;
+  const int PB = std::min(P, 64);
+  const dim3 grid((unsigned)H, (unsigned)((P + PB - 1) / PB));
+  const int threads = ((PB * 8 + 31) / 32) * 32;
+  const size_t smem = (size_t)16 * (2 + 2 * N + 2 * PB) * 4;
+  const int need = (N + 7) / 8;
+#define DSK_SCAN(R) ssd_scan<R><<<grid, threads, smem, st>>>(proj, ld_proj, 0, inner + (int)ssd_channels(sp), xbc, ld_xbc, 0, inner, inner + G * N, \
+                                                             L.dt_bias, L.A_log, L.D, state, out, inner, T, H, P, N, G, PB)
+  if (need <= 1) DSK_SCAN(1); else if (need <= 2) DSK_SCAN(2); else if (need <= 4) DSK_SCAN(4); else if (need <= 6) DSK_SCAN(6);
+  else if (need <= 8) DSK_SCAN(8); else if (need <= 12) DSK_SCAN(12); else if (need <= 16) DSK_SCAN(16); else if (need <= 24) DSK_SCAN(24);
+  else DSK_SCAN(32);
+#undef DSK_SCAN
+}
+
+static void launch_attn(const float* qa, const float* cache, float* out, int T, int H, int R, const int* ctl, int window, int ring,
+                        float scale, cudaStream_t st) {
+  const int TQ = T >= 8 ? 8 : T >= 4 ? 4 : T >= 2 ? 2 : 1, HB = 8 / TQ;
+  const dim3 grid((unsigned)((T + TQ - 1) / TQ), (unsigned)((H + HB - 1) / HB));
+  const size_t smem = ((size_t)8 * R + (size_t)32 * (R + 1)) * 4;
+  if (R <= 128) latent_swa_attn<float, 4><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ);
+  else if (R <= 256) latent_swa_attn<float, 8><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ);
+  else if (R <= 512) latent_swa_attn<float, 16><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ);
+  else latent_swa_attn<float, 32><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ);
+}
+
+// Enqueues the kernels of one chunk of T <= chunk tokens (ids in S->d_tok, first position in S->d_ctl) on `st`.
+// n_want > 0: the LM head runs on the rows listed in S->d_want -> S->logits [n_want][vocab].  trace (device, nullable):
+// [layers][T][width] copies of the residual stream after every layer.
+static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* trace, cudaStream_t st) {
+  Model* M = m->hy;
+  State* S = s->hy;
+  const dsk_hybrid_config& c = M->c;
+  const bool bf = c.quant == DSK_BF16;
+  const int W = c.dim;
+  const float mult = c.residual_mult;
+  if (bf) embed_rows<__nv_bfloat16><<<T, 256, 0, st>>>(S->d_tok, (const __nv_bfloat16*)M->embed.p, W, S->x);
+  else embed_rows<float><<<T, 256, 0, st>>>(S->d_tok, (const float*)M->embed.p, W, S->x);
+  S->launches++;
+  for (int li = 0; li < c.n_layers; li++) {
+    const HLayer& L = M->L[li];
+    const dsk_layer_spec& sp = L.sp;
+    LayerState& ls = S->L[li];
+    group_rmsnorm<float><<<T, 256, 0, st>>>(S->x, W, L.norm1, S->h, W, W, c.norm_groups, c.norm_eps, 0, 0.f, nullptr, 0);
+    S->launches++;
+    if (is_ssd(sp)) {
+      const int inner = (int)ssd_inner(sp), ch = (int)ssd_channels(sp), pw = (int)ssd_proj(sp);
+      linear(S, bf, HEPI_STORE, gp(S->h, W, L.in.p, W, S->b0, pw, T, pw, W), 1, st);
+      causal_conv_silu<<<dim3((unsigned)((ch + 127) / 128), (unsigned)T), 128, 0, st>>>(S->b0 + inner, pw, L.conv_w, L.conv_b, ls.hist, S->b1, ch, T, ch, sp.ssm_conv);
+      if (sp.ssm_conv > 1) conv_history_update<<<(ch + 127) / 128, 128, 0, st>>>(S->b0 + inner, pw, ls.hist, T, ch, sp.ssm_conv);
+      launch_scan(sp, S->b0, pw, S->b1, ch, L, ls.ssm, S->b2, T, st);
+      group_rmsnorm<float><<<T, 256, 0, st>>>(S->b2, inner, L.mnorm, S->b3, inner, inner, sp.ssm_norm_groups, c.norm_eps, 0, 0.f, nullptr, 0);
+      S->launches += 4;
+      GemmP P = gp(S->b3, inner, L.o.p, inner, S->x, W, T, W, inner);
+      P.alpha = mult;
+      linear(S, bf, HEPI_ADD, P, 1, st);
+    } else {
+      const int H = sp.att_heads, D = sp.att_dim, V = sp.att_vdim, R = sp.att_kv_rank;
+      const HLayer& O = M->L[L.owner];
+      float* cache = (float*)S->L[L.owner].cache;
+      linear(S, bf, HEPI_STORE, gp(S->h, W, L.q.p, W, S->b0, H * D, T, H * D, W), 1, st);
+      if (L.owner == li) {
+        linear(S, bf, HEPI_STORE, gp(S->h, W, L.dkv.p, W, S->b1, R, T, R, W), 1, st);
+        group_rmsnorm<float><<<T, 256, 0, st>>>(S->b1, R, L.dkv_norm, cache, R, R, 1, c.norm_eps, 0, 0.f, S->d_ctl, O.ring);
+        S->launches++;
+      }
+      {  // absorbed query: qa[t][h][:] = W_uk[h]^T q[t][h][:]
+        GemmP P = gp(S->b0, H * D, L.ukT.p, D, S->b2, H * R, T, R, D);
+        P.sA = D; P.sW = (long long)R * D; P.sC = R;
+        linear(S, bf, HEPI_STORE, P, H, st);
+      }
+      launch_attn(S->b2, cache, S->b3, T, H, R, S->d_ctl, sp.att_window, O.ring, sp.att_scale, st);
+      S->launches++;
+      {  // value up-projection per head: ov[t][h][:] = W_uv[h] o[t][h][:]
+        GemmP P = gp(S->b3, H * R, L.uv.p, R, S->b0, H * V, T, V, R);
+        P.sA = R; P.sW = (long long)V * R; P.sC = V;
+        linear(S, bf, HEPI_STORE, P, H, st);
+      }
+      GemmP P = gp(S->b0, H * V, L.o.p, H * V, S->x, W, T, W, H * V);
+      P.alpha = mult;
+      linear(S, bf, HEPI_ADD, P, 1, st);
+    }
+    if (sp.ff_kind == DSK_FF_MOE) {
+      const int E = sp.ff_experts, top = sp.ff_top, ff = sp.ff_hidden, pairs = T * top;
+      linear(S, false, HEPI_STORE, gp(S->h, W, L.router, W, S->b0, E, T, E, W), 1, st);   // router: fp32 weights in every mode
+      moe_route<<<T, 128, (size_t)(2 * E + top) * 4, st>>>(S->b0, L.correction, E, top, sp.ff_router_scale, S->d_idx, S->wgt);
+      S->launches++;
+      GemmP G = gp(S->h, W, L.gate_s.p, W, S->b2, ff, pairs, ff, W);
+      G.W2 = L.up_s.p; G.sW = (long long)ff * W; G.lim = sp.ff_limit;
+      GemmP Dn = gp(S->b2, ff, L.down_s.p, ff, S->b3, W, pairs, W, ff);
+      Dn.sW = (long long)ff * W;
+      if (T <= 4) {
+        G.z_expert = S->d_idx; G.z_adiv = top; Dn.z_expert = S->d_idx; Dn.z_adiv = 1;
+        linear(S, bf, HEPI_GLU, G, pairs, st);
+        linear(S, bf, HEPI_STORE, Dn, pairs, st);
+      } else {
+        moe_plan<<<1, 256, (size_t)2 * E * 4, st>>>(S->d_idx, pairs, E, 64, S->d_perm, S->d_tiles, S->d_ntiles);
+        S->launches++;
+        G.tiles = S->d_tiles; G.n_tiles = S->d_ntiles; G.a_map = S->d_perm; G.a_div = top; G.c_map = S->d_perm;
+        Dn.tiles = S->d_tiles; Dn.n_tiles = S->d_ntiles; Dn.a_map = S->d_perm; Dn.a_div = 1; Dn.c_map = S->d_perm;
+        const int cap = std::min(S->max_tiles, pairs / 64 + E + 1);
+        linear(S, bf, HEPI_GLU, G, 1, st, cap);
+        linear(S, bf, HEPI_STORE, Dn, 1, st, cap);
+      }
+      moe_combine<<<T, 256, 0, st>>>(S->x, W, S->b3, S->wgt, top, W, mult);
+      S->launches++;
+    }
+    if (c.side_dim > 0) {
+      const int sd = c.side_dim;
+      GemmP P = gp(S->x, W, L.sgate.p, W, S->b1, sd, T, sd, W);
+      P.aux = M->side_embed.p; P.aux_row = S->d_tok; P.aux_ld = sd * c.n_layers; P.aux_off = li * sd;
+      linear(S, bf, HEPI_GELU_MUL, P, 1, st);
+      linear(S, bf, HEPI_STORE, gp(S->b1, sd, L.sproj.p, sd, S->h, W, T, W, sd), 1, st);
+      group_rmsnorm<float><<<T, 256, 0, st>>>(S->h, W, L.snorm, S->x, W, W, 1, c.norm_eps, 1, mult, nullptr, 0);
+      S->launches++;
+    }
+    if (trace) CKL(cudaMemcpyAsync(trace + (size_t)li * T * W, S->x, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st));
+  }
+  if (n_want > 0) {
+    group_rmsnorm<float><<<T, 256, 0, st>>>(S->x, W, M->final_norm, S->h, W, W, c.norm_groups, c.norm_eps, 0, 0.f, nullptr, 0);
+    GemmP P = gp(S->h, W, M->embed.p, W, S->logits, c.vocab_size, n_want, c.vocab_size, W);
+    P.a_map = S->d_want; P.alpha = c.logit_scale;
+    linear(S, bf, HEPI_STORE, P, 1, st);
+    S->launches++;
+  }
+  CKL(cudaGetLastError());
+  return 0;
+}
+
+// tokens [n] at positions pos0.. of the state's sequence; want: ascending indices into tokens whose logits go to host_logits
+// [n_want][vocab]; host_layers (nullable): [layers][n][width] residual stream after every layer.
+static int forward_chunk(dsk_model* m, dsk_state* s, const int32_t* tokens, int n, int pos0, const int32_t* want, int n_want,
+                         float* host_logits, float* host_layers) {
+  Model* M = m->hy;
+  State* S = s->hy;
+  const dsk_hybrid_config& c = M->c;
+  if (n <= 0) return fail(-4, "empty chunk");
+  if (pos0 == 0) { if (state_reset(s)) return -2; }
+  else if (pos0 != S->next_pos) return fail(-4, "chunk starts at position %d but the state's sequence is at %d (recurrent state cannot be rewound; position 0 starts a new sequence)", pos0, S->next_pos);
+  for (int i = 0; i < n; i++) if (tokens[i] < 0 || tokens[i] >= c.vocab_size) return fail(-4, "token %d out of range", tokens[i]);
+  for (int i = 0; i < n_want; i++) if (want[i] < 0 || want[i] >= n || (i && want[i] <= want[i - 1])) return fail(-4, "wanted rows must be ascending indices into the chunk");
+  for (const HLayer& L : M->L)   // a ring cache shortened to max_seq_len holds no position beyond it
+    if (L.sp.mixer == DSK_MIX_LATENT_SWA && M->L[L.owner].ring < L.sp.att_window - 1 + S->chunk && pos0 + n > M->L[L.owner].ring)
+      return fail(-4, "position %d does not fit the latent cache (max_seq_len %d)", pos0 + n - 1, c.max_seq_len);
+  float* d_trace = nullptr;
+  int wi = 0;
+  for (int o = 0; o < n; o += S->chunk) {
+    const int T = std::min(S->chunk, n - o);
+    CK(cudaStreamSynchronize(s->stream));   // the pinned staging buffers are reused
+    memcpy(S->h_tok, tokens + o, (size_t)T * 4);
+    int nw = 0;
+    while (wi + nw < n_want && want[wi + nw] < o + T) { S->h_want[nw] = want[wi + nw] - o; nw++; }
+    CK(cudaMemcpyAsync(S->d_tok, S->h_tok, (size_t)T * 4, cudaMemcpyHostToDevice, s->stream));
+    if (nw) CK(cudaMemcpyAsync(S->d_want, S->h_want, (size_t)nw * 4, cudaMemcpyHostToDevice, s->stream));
+    set_ctl<<<1, 1, 0, s->stream>>>(S->d_ctl, pos0 + o);
+    if (host_layers) { CK(cudaMalloc((void**)&d_trace, (size_t)c.n_layers * T * c.dim * 4)); }
+    if (enqueue_chunk(m, s, T, nw, d_trace, s->stream)) { if (d_trace) cudaFree(d_trace); return -2; }
+    if (nw && host_logits) CK(cudaMemcpyAsync(host_logits + (size_t)wi * c.vocab_size, S->logits, (size_t)nw * c.vocab_size * 4, cudaMemcpyDeviceToHost, s->stream));
+    if (nw) {   // the last wanted row stays in the state for the samplers
+      CK(cudaMemcpyAsync(s->logits, S->logits + (size_t)(nw - 1) * c.vocab_size, (size_t)c.vocab_size * 4, cudaMemcpyDeviceToDevice, s->stream));
+      argmax_row<<<1, 1024, 0, s->stream>>>(s->logits, c.vocab_size, s->ctrl, nullptr, nullptr, 0);
+    }
+    if (host_layers) {
+      CK(cudaStreamSynchronize(s->stream));
+      for (int l = 0; l < c.n_layers; l++)
+        CK(cudaMemcpy(host_layers + ((size_t)l * n + o) * c.dim, d_trace + (size_t)l * T * c.dim, (size_t)T * c.dim * 4, cudaMemcpyDeviceToHost));
+      cudaFree(d_trace); d_trace = nullptr;
+    }
+    wi += nw;
+  }
+  CK(cudaStreamSynchronize(s->stream));
+  CK(cudaGetLastError());
+  S->next_pos = pos0 + n;
+  s->last_pos = pos0 + n - 1;
+  s->have_logits = n_want > 0 && want[n_want - 1] == n - 1;
+  return 0;
+}
+
+// greedy loop on the device: arg-max of the logits in the state -> next token -> one-token chunk -> logits, n_steps times,
+// without a host round trip.  The step is captured once per state as a CUDA graph (positions advance in device memory).
+static int decode_greedy(dsk_model* m, dsk_state* s, int start_pos, int n_steps, int32_t* out_tokens, float* elapsed_ms) {
+  Model* M = m->hy;
+  State* S = s->hy;
+  const dsk_hybrid_config& c = M->c;
+  if (start_pos != S->next_pos) return fail(-4, "dsk_decode_greedy: start_pos %d must follow the state's sequence (at %d)", start_pos, S->next_pos);
+  const int one = 0;
+  CK(cudaMemcpyAsync(S->d_want, &one, 4, cudaMemcpyHostToDevice, s->stream));
+  set_ctl<<<1, 1, 0, s->stream>>>(S->d_ctl, start_pos);
+  CK(cudaMemsetAsync(s->step, 0, sizeof(int), s->stream));
+  CK(cudaStreamSynchronize(s->stream));
+  if (!S->step_graph) {
+    cudaGraph_t g = nullptr;
+    CK(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+    greedy_feed<<<1, 1, 0, s->stream>>>(s->ctrl, S->d_tok, s->token_log, s->step);
+    int rc = enqueue_chunk(m, s, 1, 1, nullptr, s->stream);
+    cudaMemcpyAsync(s->logits, S->logits, (size_t)c.vocab_size * 4, cudaMemcpyDeviceToDevice, s->stream);
+    argmax_row<<<1, 1024, 0, s->stream>>>(s->logits, c.vocab_size, s->ctrl, nullptr, nullptr, 0);
+    advance_ctl<<<1, 1, 0, s->stream>>>(S->d_ctl, 1);
+    cudaError_t e = cudaStreamEndCapture(s->stream, &g);
+    if (rc || e != cudaSuccess) return fail(-2, "capturing the decode step failed: %s", cudaGetErrorString(e));
+    CK(cudaGraphInstantiate(&S->step_graph, g, 0));
+    cudaGraphDestroy(g);
+  }
+  CK(cudaEventRecord(s->ev0, s->stream));
+  for (int i = 0; i < n_steps; i++) CK(cudaGraphLaunch(S->step_graph, s->stream));
+  CK(cudaEventRecord(s->ev1, s->stream));
+  CK(cudaStreamSynchronize(s->stream));
+  if (elapsed_ms) CK(cudaEventElapsedTime(elapsed_ms, s->ev0, s->ev1));
+  if (out_tokens) CK(cudaMemcpy(out_tokens, s->token_log, (size_t)n_steps * 4, cudaMemcpyDeviceToHost));
+  S->next_pos = start_pos + n_steps;
+  s->last_pos = S->next_pos - 1;
+  s->have_logits = true;
+  return 0;
+}
+
+}  // namespace hyb

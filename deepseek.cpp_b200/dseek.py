@@ -71,6 +71,24 @@ def write_shard(path: str, tensors: Dict[str, Tuple[str, np.ndarray]], metadata:
             f.write(arr.tobytes() if arr.nbytes < (1 << 26) else memoryview(arr).cast("B"))
 
 
+def read_shard(path: str):
+    """One shard file (the safetensors layout): returns (metadata dict | None, {name: DseekTensor}) over a zero-copy memmap."""
+    mm = np.memmap(path, dtype=np.uint8, mode="r")
+    (hlen,) = struct.unpack("<Q", mm[:8].tobytes())
+    header = json.loads(mm[8 : 8 + hlen].tobytes().decode("utf-8"))
+    base = 8 + hlen
+    metadata, tensors = None, {}
+    for name, val in header.items():
+        if name == "__metadata__":
+            metadata = val
+            continue
+        b, e = val["data_offsets"]
+        dt = _DTYPES[val["dtype"]]
+        arr = mm[base + b : base + e].view(dt).reshape(val["shape"])
+        tensors[name] = DseekTensor(name, val["dtype"], tuple(val["shape"]), arr)
+    return metadata, tensors
+
+
 def read_dir(dirname: str):
     """Returns (metadata dict, {name: DseekTensor}) with zero-copy memmaps."""
     files = sorted(os.path.join(dirname, f) for f in os.listdir(dirname))
@@ -79,19 +97,23 @@ def read_dir(dirname: str):
     metadata = None
     tensors: Dict[str, DseekTensor] = {}
     for idx, path in enumerate(files):
-        mm = np.memmap(path, dtype=np.uint8, mode="r")
-        (hlen,) = struct.unpack("<Q", mm[:8].tobytes())
-        header = json.loads(mm[8 : 8 + hlen].tobytes().decode("utf-8"))
-        base = 8 + hlen
-        for name, val in header.items():
-            if name == "__metadata__":
-                if idx == 0:
-                    metadata = val
-                continue
-            b, e = val["data_offsets"]
-            dt = _DTYPES[val["dtype"]]
-            arr = mm[base + b : base + e].view(dt).reshape(val["shape"])
-            tensors[name] = DseekTensor(name, val["dtype"], tuple(val["shape"]), arr)
+        md, ts = read_shard(path)
+        if idx == 0:
+            metadata = md
+        tensors.update(ts)
     if metadata is None:
         raise ValueError("first shard has no __metadata__")
     return metadata, tensors
+
+
+def read_config_dir(dirname: str):
+    """A checkpoint directory of the config.json + *.safetensors kind (layer-list models): returns (config dict, tensors)."""
+    with open(os.path.join(dirname, "config.json")) as f:
+        config = json.load(f)
+    tensors: Dict[str, DseekTensor] = {}
+    for f in sorted(os.listdir(dirname)):
+        if f.endswith(".safetensors"):
+            tensors.update(read_shard(os.path.join(dirname, f))[1])
+    if not tensors:
+        raise FileNotFoundError(f"no *.safetensors in {dirname}")
+    return config, tensors

@@ -22,7 +22,9 @@ import sys  # noqa: E402
 sys.path.insert(0, HERE)
 import dseek  # noqa: E402
 
-QUANT_IDS = {"fp32": 0, "fp16": 1, "f8e5m2": 2, "q2_k": 3, "q3_k": 4}
+QUANT_IDS = {"fp32": 0, "fp16": 1, "f8e5m2": 2, "q2_k": 3, "q3_k": 4, "bf16": 5}
+MIX_SSD, MIX_LATENT_SWA = 0, 1
+FF_NONE, FF_MOE = 0, 1
 HYDRATE_KV_CACHE, OUTPUT_LOGITS = 0, 1
 
 f32p = C.POINTER(C.c_float)
@@ -81,8 +83,72 @@ class Config(C.Structure):
         return c
 
 
+class LayerSpec(C.Structure):
+    """dsk_layer_spec (include/dsk.h): one layer of a layer-list model."""
+    _fields_ = [(n, C.c_int) for n in ("mixer", "ssm_heads", "ssm_vdim", "ssm_state", "ssm_groups", "ssm_conv", "ssm_norm_groups",
+                                       "att_heads", "att_dim", "att_vdim", "att_kv_rank", "att_window", "att_kv_from")] + \
+               [("att_scale", C.c_float)] + [(n, C.c_int) for n in ("ff_kind", "ff_experts", "ff_top", "ff_hidden")] + \
+               [("ff_limit", C.c_float), ("ff_router_scale", C.c_float)]
+
+
+class HybridConfig(C.Structure):
+    """dsk_hybrid_config (include/dsk.h)."""
+    _fields_ = [(n, C.c_int) for n in ("dim", "vocab_size", "n_layers", "max_seq_len", "quant", "chunk")] + \
+               [("norm_eps", C.c_float), ("norm_groups", C.c_int), ("residual_mult", C.c_float), ("logit_scale", C.c_float),
+                ("side_dim", C.c_int)]
+
+
+# mixer "type" strings of a layer-list config.json -> mixer kernel family.  Two names may map to one mechanism.
+MIXER_TYPES = {"mamba2": MIX_SSD, "mamba2_2": MIX_SSD, "latent_attention": MIX_LATENT_SWA}
+
+
+def hybrid_from_config(cfg: dict, quant: str = "bf16", max_seq_len: int = 0, chunk: int = 256):
+    """config.json of a layer-list model -> (HybridConfig, LayerSpec array).  Every size and constant comes from the file;
+    keys the file does not have switch the corresponding part off (no token_side: no per-layer token input; mlp null: none)."""
+    hc = HybridConfig()
+    layers = cfg["layers"]
+    hc.dim, hc.vocab_size, hc.n_layers = int(cfg["width"]), int(cfg["vocab"]), len(layers)
+    hc.quant, hc.chunk = QUANT_IDS[quant], int(chunk)
+    hc.max_seq_len = int(max_seq_len) if max_seq_len else 1 << 30
+    norm = cfg.get("norm") or {}
+    hc.norm_eps, hc.norm_groups = float(norm.get("eps", 1e-5)), int(norm.get("groups", 1))
+    hc.residual_mult, hc.logit_scale = float(cfg.get("residual_mult", 1.0)), float(cfg.get("logit_scale", 1.0))
+    hc.side_dim = int((cfg.get("token_side") or {}).get("dim", 0))
+    specs = (LayerSpec * len(layers))()
+    for i, lc in enumerate(layers):
+        sp, mx = specs[i], lc["mixer"]
+        if lc["type"] not in MIXER_TYPES:
+            raise DskError(f"layer {i}: unknown mixer type {lc['type']!r}")
+        sp.mixer = MIXER_TYPES[lc["type"]]
+        sp.att_kv_from = -1
+        if sp.mixer == MIX_SSD:
+            sp.ssm_heads, sp.ssm_vdim, sp.ssm_state = int(mx["heads"]), int(mx["vdim"]), int(mx["state"])
+            sp.ssm_groups, sp.ssm_conv = int(mx.get("groups", 1)), int(mx["conv"])
+            sp.ssm_norm_groups = int(mx.get("norm_groups", 1))
+        else:
+            sp.att_heads, sp.att_dim, sp.att_vdim = int(mx["heads"]), int(mx["dim"]), int(mx["vdim"])
+            sp.att_kv_rank, sp.att_scale = int(mx["kv_rank"]), float(mx["scale"])
+            mask = mx.get("mask") or {}
+            sp.att_window = int(mask["size"]) if "size" in mask else 1 << 30      # no window: every earlier token is visible
+            sp.att_kv_from = int(mx["kv_from"]) if mx.get("kv_from") is not None else -1
+        ff = lc.get("mlp")
+        if ff:
+            if ff.get("kind", "moe") != "moe":
+                raise DskError(f"layer {i}: unknown feed-forward kind {ff.get('kind')!r}")
+            sp.ff_kind = FF_MOE
+            sp.ff_experts, sp.ff_top = int(ff["router"]["experts"]), int(ff["router"]["top"])
+            sp.ff_router_scale = float(ff["router"].get("scale", 1.0))
+            sp.ff_hidden, sp.ff_limit = int(ff["expert"]["ff"]), float(ff["expert"]["limit"])
+        else:
+            sp.ff_kind = FF_NONE
+    return hc, specs
+
+
+# config.json "architecture" -> builder of the C-ABI model description (the DeepSeek families come as .dseek metadata instead)
+ARCHITECTURES = {"Desarax": hybrid_from_config}
+
 _lib = None
-ABI_VERSION = 3   # DSK_ABI_VERSION (include/dsk.h)
+ABI_VERSION = 4   # DSK_ABI_VERSION (include/dsk.h)
 
 
 def build(force: bool = False) -> str:
@@ -110,6 +176,10 @@ def lib():
         L.dsk_last_error.restype = C.c_char_p
         L.dsk_model_create.restype = C.c_void_p
         L.dsk_model_create.argtypes = [C.POINTER(Config), C.c_int, C.c_int]
+        L.dsk_model_create_hybrid.restype = C.c_void_p
+        L.dsk_model_create_hybrid.argtypes = [C.POINTER(HybridConfig), C.POINTER(LayerSpec), C.c_int, C.c_int]
+        L.dsk_forward_chunk.argtypes = [C.c_void_p, C.c_void_p, i32p, C.c_int, C.c_int, i32p, C.c_int, f32p, f32p]
+        L.dsk_state_reset.argtypes = [C.c_void_p]
         L.dsk_model_destroy.argtypes = [C.c_void_p]
         L.dsk_upload_tensor.argtypes = [C.c_void_p, C.c_char_p, C.c_int, C.POINTER(C.c_int64), C.c_void_p, C.c_size_t, C.c_int]
         L.dsk_model_finalize.argtypes = [C.c_void_p]
@@ -185,18 +255,37 @@ _DT = {"F32": 0, "F16": 1, "BF16": 2, "F8_E5M2": 3, "F8_E4M3": 4, "I32": 5, "I16
 class Model:
     """Device-resident model (the reference's YALMData + Model + InferenceState + Device::CUDA)."""
 
-    def __init__(self, cfg: Config, rank: int = 0, n_ranks: int = 1, device: Optional[int] = None):
+    def __init__(self, cfg, rank: int = 0, n_ranks: int = 1, device: Optional[int] = None, layers=None):
         init(rank if device is None else device)
         self.L = lib()
         self.cfg = cfg
-        self.h = self.L.dsk_model_create(C.byref(cfg), rank, n_ranks)
+        self.layers = layers
+        if isinstance(cfg, HybridConfig):
+            self.h = self.L.dsk_model_create_hybrid(C.byref(cfg), layers, rank, n_ranks)
+        else:
+            self.h = self.L.dsk_model_create(C.byref(cfg), rank, n_ranks)
         if not self.h:
             raise DskError(self.L.dsk_last_error().decode())
         self.s = None
         self.rank, self.n_ranks = rank, n_ranks
 
     @classmethod
-    def from_dir(cls, dirname: str, context: int = 0, rank: int = 0, n_ranks: int = 1, device: Optional[int] = None):
+    def from_dir(cls, dirname: str, context: int = 0, rank: int = 0, n_ranks: int = 1, device: Optional[int] = None,
+                 quant: str = "bf16", chunk: int = 256):
+        """A .dseek directory (DeepSeek families, chosen by its metadata) or a config.json + safetensors directory (chosen by
+        the file's "architecture").  `quant` / `chunk` apply to the latter: fp32 or bf16 matrices, tokens per prefill step."""
+        if os.path.exists(os.path.join(dirname, "config.json")):
+            config, tensors = dseek.read_config_dir(dirname)
+            arch = config.get("architecture")
+            if arch not in ARCHITECTURES:
+                raise DskError(f"unknown architecture {arch!r} (known: {sorted(ARCHITECTURES)})")
+            hc, specs = ARCHITECTURES[arch](config, quant=quant, max_seq_len=context, chunk=chunk)
+            m = cls(hc, rank, n_ranks, device, layers=specs)
+            m.metadata = config
+            for name, t in tensors.items():
+                m.upload(name, t.dtype, t.shape, t.data)
+            m.finalize()
+            return m
         md, tensors = dseek.read_dir(dirname)
         m = cls(Config.from_metadata(md, context), rank, n_ranks, device)
         m.metadata = md
@@ -242,6 +331,22 @@ class Model:
         lp = _fp(self._logits) if (mode and want_logits) else None
         _ck(self.L.dsk_forward(self.h, self.s, token, pos, mode, lp, C.byref(am) if mode else None))
         return (self._logits if lp is not None else None), (am.value if mode else None)
+
+    def forward_chunk(self, tokens, pos0: int, want=(), layers: bool = False):
+        """A portion of consecutive tokens starting at position pos0 (dsk_forward_chunk).  Returns the logits of the `want`
+        rows [len(want), vocab] (and, with layers=True, the residual stream after every layer [layers, n, dim])."""
+        tok = np.ascontiguousarray(tokens, dtype=np.int32)
+        w = np.ascontiguousarray(list(want), dtype=np.int32)
+        out = np.zeros((len(w), self.cfg.vocab_size), dtype=np.float32)
+        tr = np.zeros((self.cfg.n_layers, len(tok), self.cfg.dim), dtype=np.float32) if layers else None
+        _ck(self.L.dsk_forward_chunk(self.h, self.s, tok.ctypes.data_as(i32p), len(tok), pos0,
+                                     w.ctypes.data_as(i32p) if len(w) else None, len(w),
+                                     _fp(out) if len(w) else None, _fp(tr) if layers else None))
+        return (out, tr) if layers else out
+
+    def reset(self):
+        """Gives back the sequence the state holds; the next call starts at position 0."""
+        _ck(self.L.dsk_state_reset(self.s))
 
     def copy_embedding(self, token: int):
         _ck(self.L.dsk_copy_embedding(self.h, self.s, token))

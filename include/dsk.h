@@ -20,10 +20,11 @@
 extern "C" {
 #endif
 
-#define DSK_ABI_VERSION 3
+#define DSK_ABI_VERSION 4
 
 /* Quant: src/codec.h:79-85 (same numbering) */
-enum { DSK_F32 = 0, DSK_F16 = 1, DSK_F8E5M2 = 2, DSK_Q2_K = 3, DSK_Q3_K = 4 };
+enum { DSK_F32 = 0, DSK_F16 = 1, DSK_F8E5M2 = 2, DSK_Q2_K = 3, DSK_Q3_K = 4,
+       DSK_BF16 = 5 /* bfloat16 matrices, fp32 activations: layer-list models only */ };
 /* CodecDType: src/codec.h:62-72 (same numbering; .dseek payloads use F32, F16, F8E5M2 and U8) */
 enum { DSK_DT_F32 = 0, DSK_DT_F16 = 1, DSK_DT_BF16 = 2, DSK_DT_F8E5M2 = 3, DSK_DT_F8E4M3 = 4, DSK_DT_I32 = 5, DSK_DT_I16 = 6,
        DSK_DT_I8 = 7, DSK_DT_U8 = 8 };
@@ -52,6 +53,39 @@ typedef struct dsk_config {
   int use_mla;               /* 1: true-MLA blocks (BlockMLA, src/model.h:366-453): wc / wq_rope_b / wv_b tensors, latent KV cache */
 } dsk_config;
 
+/* ---- layer-list ("hybrid") models ------------------------------------------------------------------------------
+ * A second model family next to the DeepSeek blocks above: the checkpoint's config.json lists the layers one by one, each
+ * with a token mixer and an optional routed feed-forward, so every layer carries its own sizes.  The reference has no such
+ * model; it runs through the same model / state / forward / sampling entry points.  (The Desarax design is of this family.)
+ *   DSK_MIX_SSD         state-space-duality recurrence (Mamba-2 form): input projection [z | x | B | C | dt], depthwise causal
+ *                       convolution + SiLU over [x | B | C], per-head state S (state x vdim) with scalar decay, gate, grouped
+ *                       RMS norm, output projection.  Carries S and the last conv - 1 convolution inputs per sequence.
+ *   DSK_MIX_LATENT_SWA  softmax attention over a sliding window of cached low-rank latents (no positional rotation): keys and
+ *                       values are per-head up-projections of the normalised latent; att_kv_from >= 0 reads another layer's
+ *                       latent cache instead of projecting its own.
+ * Every layer: h = norm(x) (RMS norm in norm_groups parts); x += residual_mult * (mixer(h) + ff(h)); then, with side_dim > 0,
+ * a per-layer token embedding gated by gelu_tanh(side.gate x) is projected, RMS-normed and added (x += residual_mult * ...). */
+enum { DSK_MIX_SSD = 0, DSK_MIX_LATENT_SWA = 1 };
+enum { DSK_FF_NONE = 0, DSK_FF_MOE = 1 };
+typedef struct dsk_layer_spec {
+  int mixer;                                                            /* DSK_MIX_* */
+  int ssm_heads, ssm_vdim, ssm_state, ssm_groups, ssm_conv, ssm_norm_groups;   /* DSK_MIX_SSD */
+  int att_heads, att_dim, att_vdim, att_kv_rank, att_window, att_kv_from;      /* DSK_MIX_LATENT_SWA; att_kv_from < 0: own latent */
+  float att_scale;
+  int ff_kind, ff_experts, ff_top, ff_hidden;                           /* DSK_FF_MOE: sigmoid router with selection bias, */
+  float ff_limit, ff_router_scale;                                      /* clamped GLU experts g*sigmoid(1.702 g)*(u + 1)   */
+} dsk_layer_spec;
+typedef struct dsk_hybrid_config {
+  int dim, vocab_size, n_layers;
+  int max_seq_len;           /* positions a sequence may reach when a latent window does not fit the ring cache */
+  int quant;                 /* DSK_F32 (everything in fp32) or DSK_BF16 */
+  int chunk;                 /* tokens one step processes at most (longer calls are cut into portions of this size) */
+  float norm_eps;
+  int norm_groups;
+  float residual_mult, logit_scale;
+  int side_dim;              /* per-layer token input width, 0 = none */
+} dsk_hybrid_config;
+
 typedef struct dsk_model dsk_model;
 typedef struct dsk_state dsk_state;
 
@@ -72,6 +106,9 @@ int dsk_device_info(char* name128, int* sm_count, size_t* hbm_bytes);
  * the ranks; wq_a / wkv_a / the gate / norms / embedding stay replicated.  Requires n_heads % n_ranks == 0 and
  * (n_heads / n_ranks) * v_head_dim % 256 == 0, otherwise only the experts are sharded. */
 dsk_model* dsk_model_create(const dsk_config* cfg, int rank, int n_ranks);
+/* Layer-list model of cfg->n_layers layers (rank 0 of 1 only).  Tensors are uploaded by their checkpoint names through
+ * dsk_upload_tensor (BF16 or F32 payloads; matrices are kept in cfg->quant), then dsk_model_finalize checks completeness. */
+dsk_model* dsk_model_create_hybrid(const dsk_hybrid_config* cfg, const dsk_layer_spec* layers, int rank, int n_ranks);
 /* What dsk_model_create decided for this rank: tensor_parallel (0/1), local attention heads, local routed experts. */
 int dsk_model_sharding(const dsk_model* m, int* tensor_parallel, int* local_heads, int* local_experts);
 void dsk_model_destroy(dsk_model* m);
@@ -111,6 +148,16 @@ int dsk_kv_write(dsk_model* m, int layer, int which, const uint16_t* src, size_t
  * host_logits (vocab floats, nullable) receives s.logits(); argmax (nullable) receives
  * Sampler::sample_argmax (src/sampler.cpp:28-39) computed on device. */
 int dsk_forward(dsk_model* m, dsk_state* s, int token, int pos, int mode, float* host_logits, int* argmax);
+/* A portion of n_tokens consecutive tokens of the state's sequence, starting at position pos0 (prefill batching; n_tokens = 1
+ * is a decode step).  want: ascending indices into `tokens` whose logits are copied to host_logits [n_want][vocab] (nullable);
+ * host_layers (nullable, layer-list models only): [layers][n_tokens][dim] residual stream after every layer.  Layer-list
+ * models run the portion through their chunk kernels (cut into dsk_hybrid_config::chunk tokens at most) and continue from the
+ * recurrent state and latent caches in `s`: pos0 must follow the previous call, pos0 == 0 starts a new sequence.  DeepSeek
+ * models run one dsk_forward per token (their hydrate loop). */
+int dsk_forward_chunk(dsk_model* m, dsk_state* s, const int32_t* tokens, int n_tokens, int pos0, const int32_t* want, int n_want,
+                      float* host_logits, float* host_layers);
+/* Gives back what the state's sequence holds (recurrent state, convolution history, latent caches); the next call starts at 0. */
+int dsk_state_reset(dsk_state* s);
 /* Model::_copy_embedding — src/infer.cpp:1217-1263. */
 int dsk_copy_embedding(dsk_model* m, dsk_state* s, int token);
 /* Block::block(state, pos, kv_sink, kv_pos, kv_len) — src/model.cpp:290-322 -> _block_cpu src/infer.cpp:810-932. */
