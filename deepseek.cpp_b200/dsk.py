@@ -267,6 +267,7 @@ class Model:
         if not self.h:
             raise DskError(self.L.dsk_last_error().decode())
         self.s = None
+        self._extra_states = []
         self.rank, self.n_ranks = rank, n_ranks
 
     @classmethod
@@ -332,21 +333,29 @@ class Model:
         _ck(self.L.dsk_forward(self.h, self.s, token, pos, mode, lp, C.byref(am) if mode else None))
         return (self._logits if lp is not None else None), (am.value if mode else None)
 
-    def forward_chunk(self, tokens, pos0: int, want=(), layers: bool = False):
+    def new_state(self):
+        """One more sequence state of this model (dsk_state_create); pass it as `state=` to forward_chunk / reset."""
+        h = self.L.dsk_state_create(self.h)
+        if not h:
+            raise DskError(self.L.dsk_last_error().decode())
+        self._extra_states.append(h)
+        return h
+
+    def forward_chunk(self, tokens, pos0: int, want=(), layers: bool = False, state=None):
         """A portion of consecutive tokens starting at position pos0 (dsk_forward_chunk).  Returns the logits of the `want`
         rows [len(want), vocab] (and, with layers=True, the residual stream after every layer [layers, n, dim])."""
         tok = np.ascontiguousarray(tokens, dtype=np.int32)
         w = np.ascontiguousarray(list(want), dtype=np.int32)
         out = np.zeros((len(w), self.cfg.vocab_size), dtype=np.float32)
         tr = np.zeros((self.cfg.n_layers, len(tok), self.cfg.dim), dtype=np.float32) if layers else None
-        _ck(self.L.dsk_forward_chunk(self.h, self.s, tok.ctypes.data_as(i32p), len(tok), pos0,
+        _ck(self.L.dsk_forward_chunk(self.h, state or self.s, tok.ctypes.data_as(i32p), len(tok), pos0,
                                      w.ctypes.data_as(i32p) if len(w) else None, len(w),
                                      _fp(out) if len(w) else None, _fp(tr) if layers else None))
         return (out, tr) if layers else out
 
-    def reset(self):
+    def reset(self, state=None):
         """Gives back the sequence the state holds; the next call starts at position 0."""
-        _ck(self.L.dsk_state_reset(self.s))
+        _ck(self.L.dsk_state_reset(state or self.s))
 
     def copy_embedding(self, token: int):
         _ck(self.L.dsk_copy_embedding(self.h, self.s, token))
@@ -432,6 +441,9 @@ class Model:
         return self.L.dsk_launches_per_forward(self.h, mode)
 
     def close(self):
+        for h in self._extra_states:
+            self.L.dsk_state_destroy(h)
+        self._extra_states = []
         if self.s:
             self.L.dsk_state_destroy(self.s)
             self.s = None
