@@ -1,0 +1,80 @@
+"""CPU-side checks of the layer-list model family: config.json -> C-ABI description, the checkpoint reader, and the float64
+oracle's own invariants (what a sequence carries is enough to continue it; a window hides what lies outside it)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+
+@pytest.fixture(scope="module")
+def ho():
+    import hybrid_oracle
+    return hybrid_oracle
+
+
+def test_config_to_layer_specs(ho):
+    import dsk
+    cfg = ho.small_config()
+    hc, specs = dsk.ARCHITECTURES[cfg["architecture"]](cfg, quant="fp32", max_seq_len=99, chunk=8)
+    assert (hc.dim, hc.vocab_size, hc.n_layers, hc.max_seq_len, hc.chunk, hc.norm_groups, hc.side_dim) == (48, 61, 5, 99, 8, 3, 6)
+    assert hc.quant == dsk.QUANT_IDS["fp32"] and abs(hc.residual_mult - 0.7) < 1e-7 and abs(hc.logit_scale - 1.5) < 1e-7
+    a, s, b = specs[0], specs[1], specs[2]
+    assert (a.mixer, a.att_heads, a.att_dim, a.att_vdim, a.att_kv_rank, a.att_window, a.att_kv_from) == (dsk.MIX_LATENT_SWA, 3, 12, 20, 40, 7, -1)
+    assert (a.ff_kind, a.ff_experts, a.ff_top, a.ff_hidden) == (dsk.FF_MOE, 5, 2, 24) and abs(a.ff_limit - 1.5) < 1e-7
+    assert (s.mixer, s.ssm_heads, s.ssm_vdim, s.ssm_state, s.ssm_groups, s.ssm_conv, s.ssm_norm_groups, s.ff_kind) == (dsk.MIX_SSD, 6, 10, 12, 3, 3, 2, dsk.FF_NONE)
+    assert b.att_kv_from == 0 and specs[3].mixer == dsk.MIX_SSD        # a second type name of the same mechanism
+    del cfg["token_side"]
+    assert dsk.hybrid_from_config(cfg)[0].side_dim == 0
+    cfg["layers"][0]["type"] = "unheard_of"
+    with pytest.raises(dsk.DskError):
+        dsk.hybrid_from_config(cfg)
+
+
+def test_spec_structs_match_the_header(repo):
+    """The ctypes mirrors must have the C structs' sizes (field order is checked by the GPU tests' results)."""
+    import os
+    import subprocess
+    import tempfile
+
+    import dsk
+    with tempfile.TemporaryDirectory() as td:
+        src = os.path.join(td, "t.c")
+        open(src, "w").write('#include "dsk.h"\n#include <stdio.h>\nint main(void){printf("%zu %zu\\n", sizeof(dsk_layer_spec), sizeof(dsk_hybrid_config));return 0;}')
+        exe = os.path.join(td, "t")
+        subprocess.check_call(["gcc", "-std=c99", "-I", os.path.join(repo, "include"), src, "-o", exe])
+        a, b = map(int, subprocess.check_output([exe]).split())
+    assert (a, b) == (ctypes.sizeof(dsk.LayerSpec), ctypes.sizeof(dsk.HybridConfig))
+
+
+def test_checkpoint_roundtrip(ho, tmp_path):
+    import dseek
+    cfg = ho.small_config()
+    W = ho.random_weights(cfg, 2)
+    d = ho.write_checkpoint(str(tmp_path / "m"), cfg, W)
+    cfg2, ts = dseek.read_config_dir(d)
+    assert cfg2 == cfg and set(ts) == set(W)
+    for k, t in ts.items():
+        assert t.dtype == "BF16" and tuple(t.shape) == W[k].shape
+        assert np.array_equal(ho.bf16_to_f64(np.asarray(t.data)).reshape(W[k].shape), W[k])
+
+
+def test_oracle_window_and_carry(ho):
+    """Oracle invariants: (1) with one attention layer a token outside the window cannot change the logits, one inside does;
+    (2) the state-space carry continues a sequence: feeding a prefix to two Sequence objects and the same suffix gives equal logits."""
+    win = 4
+    cfg = {"architecture": "Desarax", "vocab": 23, "width": 16, "norm": {"eps": 1e-5, "groups": 1}, "residual_mult": 1.0, "logit_scale": 1.0,
+           "layers": [{"type": "latent_attention", "mlp": None, "mixer": {"heads": 2, "dim": 4, "vdim": 4, "kv_rank": 6, "mask": {"size": win}, "scale": 1.0}}]}
+    W = ho.random_weights(cfg, 4)
+    toks = np.arange(12) % 23
+    base = ho.run(cfg, W, toks)[0][-1]
+    out, ins = toks.copy(), toks.copy()
+    out[11 - win] += 1
+    ins[11 - win + 1] += 1
+    assert np.array_equal(ho.run(cfg, W, out)[0][-1], base)
+    assert np.abs(ho.run(cfg, W, ins)[0][-1] - base).max() > 1e-6
+    cfg2 = ho.small_config()
+    W2 = ho.random_weights(cfg2, 5)
+    full = ho.run(cfg2, W2, np.arange(20) % 61)[0]
+    seq = ho.Sequence(cfg2, W2)
+    rows = [seq.feed(int(t)) for t in np.arange(20) % 61]
+    assert np.allclose(np.array(rows), full, rtol=0, atol=1e-12)
