@@ -149,6 +149,8 @@ static std::string load_file(DseekData& d, const std::string& path, bool read_md
   return "";
 }
 
+std::string DseekData::load_shard(const std::string& path, bool lock_weights) { return load_file(*this, path, metadata.empty(), lock_weights); }
+
 std::string DseekData::load(const std::string& dirname, bool lock_weights) {
   DIR* dir = opendir(dirname.c_str());
   if (!dir) return "failed to open directory " + dirname;

@@ -22,5 +22,7 @@ struct DseekData {
   std::vector<std::pair<void*, size_t>> maps;
   // returns "" on success, else an error message
   std::string load(const std::string& dirname, bool lock_weights);
+  // one shard file (the safetensors layout), e.g. model.safetensors of a config.json checkpoint; no metadata required
+  std::string load_shard(const std::string& path, bool lock_weights);
   ~DseekData();
 };

@@ -18,6 +18,7 @@
 
 #include "../../../include/dsk.h"
 #include "dseek_loader.h"
+#include "json_min.h"
 
 static void error_usage() {
   fprintf(stderr, "Usage:   main <checkpoint_dir> [options]\n");
@@ -28,6 +29,8 @@ static void error_usage() {
   fprintf(stderr, "  -m [completion,perplexity] which mode to run in (default - completion)\n");
   fprintf(stderr, "  -T <int> sliding window context length (0 - max)\n");
   fprintf(stderr, "  -g <int> CUDA device (default 0)\n");
+  fprintf(stderr, "  -q [bf16,fp32] matrix type of config.json checkpoints (layer-list models; default bf16)\n");
+  fprintf(stderr, "  -I <ids> prompt as comma-separated token ids (checkpoints without a tokenizer)\n");
   fprintf(stderr, "Completion mode options:\n");
   fprintf(stderr, "  -n <int>    number of steps to run for in completion mode, default 256. 0 = max_seq_len, -1 = infinite\n");
   fprintf(stderr, "  -i <string> input prompt | -f <filepath> input file with prompt\n");
@@ -125,9 +128,122 @@ static dsk_config config_from(const DseekData& d, int context) {
 
 #define DSK_OK(call) do { if ((call) != 0) { fprintf(stderr, "FATAL: %s: %s\n", #call, dsk_last_error()); exit(1); } } while (0)
 
+static bool file_exists(const std::string& p) { std::ifstream f(p); return f.good(); }
+
+// ---- layer-list checkpoints: config.json ("architecture" picks the family) + model.safetensors --------------------------------------
+// Mixer "type" strings -> mixer kernels; two names may denote one mechanism.
+static int mixer_of(const std::string& type) {
+  if (type == "mamba2" || type == "mamba2_2") return DSK_MIX_SSD;
+  if (type == "latent_attention") return DSK_MIX_LATENT_SWA;
+  return -1;
+}
+static bool hybrid_config_from(const JValue& j, const std::string& quant, int context, dsk_hybrid_config* hc, std::vector<dsk_layer_spec>* specs) {
+  const JValue& layers = j.at("layers");
+  if (layers.kind != JValue::Arr || layers.arr.empty()) { fprintf(stderr, "FATAL: config.json has no layers\n"); return false; }
+  *hc = dsk_hybrid_config{};
+  hc->dim = j.integer("width", 0); hc->vocab_size = j.integer("vocab", 0); hc->n_layers = (int)layers.arr.size();
+  hc->max_seq_len = context > 0 ? context : 1 << 30;
+  hc->quant = quant == "fp32" ? DSK_F32 : DSK_BF16;
+  hc->chunk = context > 0 ? std::min(256, context) : 256;
+  hc->norm_eps = (float)j.at("norm").number("eps", 1e-5); hc->norm_groups = j.at("norm").integer("groups", 1);
+  hc->residual_mult = (float)j.number("residual_mult", 1.0); hc->logit_scale = (float)j.number("logit_scale", 1.0);
+  hc->side_dim = j.at("token_side").integer("dim", 0);
+  for (size_t i = 0; i < layers.arr.size(); i++) {
+    const JValue& lc = layers.arr[i];
+    const JValue& mx = lc.at("mixer");
+    dsk_layer_spec sp{};
+    sp.mixer = mixer_of(lc.at("type").str);
+    sp.att_kv_from = -1;
+    if (sp.mixer == DSK_MIX_SSD) {
+      sp.ssm_heads = mx.integer("heads", 0); sp.ssm_vdim = mx.integer("vdim", 0); sp.ssm_state = mx.integer("state", 0);
+      sp.ssm_groups = mx.integer("groups", 1); sp.ssm_conv = mx.integer("conv", 0); sp.ssm_norm_groups = mx.integer("norm_groups", 1);
+    } else if (sp.mixer == DSK_MIX_LATENT_SWA) {
+      sp.att_heads = mx.integer("heads", 0); sp.att_dim = mx.integer("dim", 0); sp.att_vdim = mx.integer("vdim", 0);
+      sp.att_kv_rank = mx.integer("kv_rank", 0); sp.att_scale = (float)mx.number("scale", 1.0);
+      sp.att_window = mx.at("mask").integer("size", 1 << 30); sp.att_kv_from = mx.integer("kv_from", -1);
+    } else { fprintf(stderr, "FATAL: layer %zu: unknown mixer type %s\n", i, lc.at("type").str.c_str()); return false; }
+    if (lc.has("mlp")) {
+      const JValue& ff = lc.at("mlp");
+      if (ff.has("kind") && ff.at("kind").str != "moe") { fprintf(stderr, "FATAL: layer %zu: unknown feed-forward kind %s\n", i, ff.at("kind").str.c_str()); return false; }
+      sp.ff_kind = DSK_FF_MOE;
+      sp.ff_experts = ff.at("router").integer("experts", 0); sp.ff_top = ff.at("router").integer("top", 0);
+      sp.ff_router_scale = (float)ff.at("router").number("scale", 1.0);
+      sp.ff_hidden = ff.at("expert").integer("ff", 0); sp.ff_limit = (float)ff.at("expert").number("limit", 0.0);
+    }
+    specs->push_back(sp);
+  }
+  return true;
+}
+
+
+// completion over token ids: the prompt goes through dsk_forward_chunk (prefill in portions), then the usual
+// dsk_sample -> dsk_forward loop; the ids are printed (these checkpoints carry no tokenizer).
+static int run_layer_list(const std::string& dir, const std::string& quant, const std::string& prompt_ids, int context, int device, int num_steps,
+                          float temperature, float top_p, bool lock) {
+  std::ifstream fs(dir + "/config.json");
+  std::stringstream ss; ss << fs.rdbuf();
+  const std::string text = ss.str();
+  JValue cfg; JReader jr{text.data(), text.data() + text.size(), ""};
+  if (!jr.parse(cfg) || cfg.kind != JValue::Obj) { fprintf(stderr, "FATAL: config.json: %s\n", jr.err.c_str()); return 1; }
+  const std::string arch = cfg.at("architecture").str;
+  if (arch != "Desarax") { fprintf(stderr, "FATAL: unknown architecture '%s' (known: Desarax)\n", arch.c_str()); return 1; }
+  if (quant != "bf16" && quant != "fp32") { fprintf(stderr, "FATAL: -q must be bf16 or fp32\n"); return 1; }
+  std::vector<int> enc;
+  for (size_t i = 0; i < prompt_ids.size();) {
+    size_t j = prompt_ids.find(',', i); if (j == std::string::npos) j = prompt_ids.size();
+    if (j > i) enc.push_back(atoi(prompt_ids.substr(i, j - i).c_str()));
+    i = j + 1;
+  }
+  if (enc.empty()) { fprintf(stderr, "No prompt provided (-I <ids>)\n"); return 1; }
+  dsk_hybrid_config hc; std::vector<dsk_layer_spec> specs;
+  if (!hybrid_config_from(cfg, quant, context, &hc, &specs)) return 1;
+  DseekData data;
+  std::string err = data.load_shard(dir + "/model.safetensors", lock);
+  if (!err.empty()) { fprintf(stderr, "failed to load checkpoint: %s\n", err.c_str()); return 1; }
+  std::cout << "loading " << arch << " model with quant: " << quant << std::endl;
+  DSK_OK(dsk_init(device));
+  double t0 = now_s();
+  dsk_model* model = dsk_model_create_hybrid(&hc, specs.data(), 0, 1);
+  if (!model) { fprintf(stderr, "FATAL: %s\n", dsk_last_error()); return 1; }
+  static const char* names[] = {"F32", "F16", "BF16", "F8_E5M2", "F8_E4M3", "I32", "I16", "I8", "U8"};   // CodecDType order
+  for (auto& kv : data.tensors) {
+    const DseekTensor& t = kv.second;
+    int dt = -1;
+    for (int k = 0; k < 9; k++) if (t.dtype == names[k]) dt = k;
+    DSK_OK(dsk_upload_tensor(model, t.name.c_str(), dt, t.shape, t.data, t.size, 0));
+  }
+  DSK_OK(dsk_model_finalize(model));
+  dsk_state* state = dsk_state_create(model);
+  if (!state) { fprintf(stderr, "FATAL: %s\n", dsk_last_error()); return 1; }
+  std::cout << "uploaded in " << now_s() - t0 << " s (" << dsk_model_resident_bytes(model) / 1e9 << " GB resident)" << std::endl;
+  srand((unsigned)(uint64_t)(now_s() * 1000));
+  if (num_steps <= 0) num_steps = 256;
+  const double start = now_s();
+  const int32_t last = (int32_t)enc.size() - 1;
+  DSK_OK(dsk_forward_chunk(model, state, enc.data(), (int)enc.size(), 0, &last, 1, nullptr, nullptr));
+  const double end_hydrate = now_s();
+  const size_t n_prompt = enc.size();
+  for (int i = 0; i < num_steps; i++) {
+    int tok = -1;
+    const float coin = temperature == 0.0f ? 0.f : rand() / (float)RAND_MAX;
+    DSK_OK(dsk_sample(model, state, temperature, top_p, coin, &tok));
+    enc.push_back(tok);
+    if (i + 1 < num_steps) DSK_OK(dsk_forward(model, state, tok, (int)enc.size() - 1, DSK_OUTPUT_LOGITS, nullptr, nullptr));
+  }
+  const double elapsed = now_s() - start;
+  std::cout << "\nGeneration stats:\n  " << enc.size() << " tokens\n  prefill: " << n_prompt / (end_hydrate - start) << "tok/s\n  decode: "
+            << (enc.size() - n_prompt) / (elapsed - (end_hydrate - start)) << "tok/s\n  total: " << elapsed << "s\n" << std::endl;
+  std::cout << "generated ids:";
+  for (size_t i = 0; i < enc.size(); i++) std::cout << " " << enc[i];
+  std::cout << std::endl;
+  dsk_state_destroy(state);
+  dsk_model_destroy(model);
+  return 0;
+}
+
 int main(int argc, char* argv[]) {
   if (argc < 2) error_usage();
-  std::string dir = argv[1], mode = "completion", prompt, prompt_path;
+  std::string dir = argv[1], mode = "completion", prompt, prompt_path, prompt_ids, hquant = "bf16";
   bool lock = false; int context = 0, device = 0, num_steps = 256; float temperature = 1.0f, top_p = 0.95f;
   for (int i = 2; i < argc;) {
     if (argv[i][0] != '-' || strlen(argv[i]) != 2) error_usage();
@@ -139,12 +255,15 @@ int main(int argc, char* argv[]) {
     switch (f) {
       case 'm': if (std::string("completion").rfind(v, 0) == 0) mode = "completion"; else if (std::string("perplexity").rfind(v, 0) == 0) mode = "perplexity"; else error_usage(); break;
       case 'T': context = atoi(v); break; case 'g': device = atoi(v); break; case 'n': num_steps = atoi(v); break;
+      case 'q': hquant = v; break; case 'I': prompt_ids = v; break;
       case 'i': prompt = v; break; case 'f': prompt_path = v; break; case 't': temperature = (float)atof(v); break; case 'p': top_p = (float)atof(v); break;
       default: error_usage();
     }
     i += 2;
   }
   if (!prompt_path.empty()) { std::ifstream fs(prompt_path); std::stringstream ss; ss << fs.rdbuf(); prompt = ss.str(); }
+  if (file_exists(dir + "/config.json"))
+    return run_layer_list(dir, hquant, prompt_ids, context, device, num_steps, temperature, top_p, lock);
   if (prompt.empty()) { fprintf(stderr, "No prompt provided\n"); error_usage(); }
 
   DseekData data;

@@ -339,3 +339,21 @@ def test_trace_runner(full, ho, repo, tmp_path):
         assert rel(rd(2), exp[[35]]) < tol
         assert rel(rd(3), exp_o[[29]]) < tol
         assert rel(rd(4), exp[[1]]) < tol
+
+
+def test_cli_completion(full, repo):
+    """The C++ host on a config.json checkpoint: prompt ids in (prefilled in portions), greedy ids out, equal to the device loop."""
+    import re
+    cfg, m, W, toks, exp, _ = full
+    exe = os.path.join(repo, "deepseek.cpp_b200", "main")
+    if not os.path.exists(exe):
+        subprocess.check_call(["make", "-C", os.path.dirname(exe), "main"])
+    prompt, steps = toks[:21].tolist(), 12
+    out = subprocess.run([exe, m.dir, "-I", ",".join(map(str, prompt)), "-n", str(steps), "-t", "0", "-q", "fp32", "-T", "40"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    ids = [int(v) for v in re.search(r"generated ids:([ 0-9]+)", out.stdout).group(1).split()]
+    assert ids[:len(prompt)] == prompt and len(ids) == len(prompt) + steps
+    m.forward_chunk(prompt, 0, [len(prompt) - 1])
+    dev, _ = m.decode_greedy(len(prompt), steps)
+    assert ids[len(prompt):] == dev.tolist()
