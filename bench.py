@@ -198,7 +198,7 @@ def mint_on_gpu(dsk, w, rank, n_ranks, device):
             if quant == "fp16":
                 x = x.half()
             x = x.contiguous()
-            m.upload_device(name + ".weight", "F16" if quant == "fp16" else "F32", x.shape, x.data_ptr(),
+            m.upload_device(name + ".weight", "F16" if quant == "fp16" else "F32", tuple(x.shape) if ne else tuple(x.shape[1:]), x.data_ptr(),
                             x.numel() * x.element_size())
             del x
     torch.cuda.synchronize()
@@ -612,7 +612,20 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the V2-Lite configs[1]/[2] continuity numbers")
     ap.add_argument("--profile-token", action="store_true", help="print the per-stage timeline of one token to stderr")
+    ap.add_argument("--hybrid", default="", help="instead of the headline workload: prefill / decode throughput of the layer-list family "
+                    "(Desarax design) beside the closest DeepSeek model at equal size; comma-separated sizes of hybrid_bench.SIZES, or 'all'")
     a = ap.parse_args()
+    if a.hybrid:
+        import torch
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "deepseek.cpp_b200"))
+        import dsk
+        import hybrid_bench
+        torch.cuda.set_device(0)
+        dsk.init(0)
+        sizes = tuple(hybrid_bench.SIZES) if a.hybrid == "all" else tuple(a.hybrid.split(","))
+        res = hybrid_bench.run(dsk, torch, os.path.dirname(os.path.abspath(__file__)), sys.modules[__name__], sizes=sizes, log=log)
+        emit({"hybrid_bench": res})
+        return 0
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

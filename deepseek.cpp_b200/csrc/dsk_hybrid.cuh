@@ -9,6 +9,7 @@
 //                     scaled, into the residual, or write its rows into a ring cache
 //   gemm_tiled        C = A W^T for T > 4 rows (fp32 activations, fp32 or bf16 weights, fp32 accumulate) with fused
 //                     epilogues (residual add, clamped GLU, GELU x per-token embedding) and row gather / scatter / expert tiles
+//   gemm_mma          the same contract on the tensor cores for bf16 weights (activations rounded to bf16 as they are staged)
 //   gemv_rows         the same contract for T <= 4 rows: one warp per weight row, 16-byte loads
 //   causal_conv_silu  depthwise causal convolution over the chunk continuing from the carried (taps - 1) inputs, + SiLU
 //   ssd_scan          the state-space recurrence S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x, gated by silu(z)
@@ -18,8 +19,9 @@
 //   moe_combine       residual += alpha * sum_k w_k y_k
 //
 // Numerics: the residual stream, norms, router, softmax, recurrent state, decays, step sizes and gates are fp32 in every mode;
-// DSK_BF16 models keep their matrices in bfloat16 and multiply them with fp32 activations (fp32 accumulate), DSK_F32 models
-// are fp32 throughout (plain FMA, no reduced-precision matrix mode).
+// DSK_BF16 models keep their matrices in bfloat16 and accumulate in fp32: decode-sized products multiply them with the fp32
+// activations, larger ones round the activations to bfloat16 on their way into the tensor cores.  DSK_F32 models are fp32
+// throughout (plain FMA, no reduced-precision matrix mode).
 #pragma once
 
 #include <cuda_bf16.h>
@@ -242,6 +244,142 @@ __global__ void __launch_bounds__(256) gemm_tiled(const GemmP P) {
   }
 }
 
+// Tensor-core variant for bf16 weights and more than a handful of rows: 128 x 128 tile of A W^T per CTA (K in steps of 32), the
+// fp32 activations rounded to bf16 while they are staged, mma.sync m16n8k16 bf16 x bf16 -> fp32.  8 warps as 2 (rows) x 4
+// (columns), a 64 x 32 warp tile.  Same row maps, expert tiles, batches and epilogues as gemm_tiled.  For the GLU epilogue the
+// 128 staged weight rows alternate, in granules of 8, between the gate and the up matrix, so a thread holds both values of an
+// output element in neighbouring accumulators and a CTA produces 64 output columns.
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(256) gemm_mma(const GemmP P) {
+  typedef __nv_bfloat16 bf;
+  constexpr int BM = 128, BT = 128, BK = 32, PITCH = BK + 8;
+  constexpr bool DUAL = EPI == HEPI_GLU;
+  constexpr int BN = DUAL ? 64 : 128;
+  __shared__ __align__(16) bf As[BM][PITCH];
+  __shared__ __align__(16) bf Bs[BT][PITCH];
+  __shared__ int rowsA[BM], rowsC[BM];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  long long aoff = (long long)blockIdx.z * P.sA, woff = (long long)blockIdx.z * P.sW, coff = (long long)blockIdx.z * P.sC;
+  int row0, nrows;
+  if (P.tiles) {
+    if ((int)blockIdx.y >= *P.n_tiles) return;
+    const int4 t = P.tiles[blockIdx.y];
+    woff = (long long)t.x * P.sW;
+    row0 = t.y;
+    nrows = t.z;
+  } else {
+    row0 = blockIdx.y * BM;
+    nrows = min(BM, P.M - row0);
+  }
+  if (tid < BM) {
+    const int i = row0 + tid;
+    const bool ok = tid < nrows;
+    rowsA[tid] = ok ? (P.a_map ? P.a_map[i] / P.a_div : i) : -1;
+    rowsC[tid] = ok ? (P.c_map ? P.c_map[i] : i) : -1;
+  }
+  __syncthreads();
+  const int n0 = blockIdx.x * BN;
+  const bf* __restrict__ W = reinterpret_cast<const bf*>(P.W) + woff;
+  const bf* __restrict__ W2 = DUAL ? reinterpret_cast<const bf*>(P.W2) + woff : nullptr;
+  const float* __restrict__ A = P.A + aoff;
+  // staging: thread -> (row, 16 consecutive k)
+  const int lr = tid >> 1, lk = (tid & 1) * 16;
+  const int ar = rowsA[lr];
+  int wrow;
+  const bf* wsrc = W;
+  if (DUAL) { const int g = lr >> 3; wrow = n0 + (g >> 1) * 8 + (lr & 7); wsrc = (g & 1) ? W2 : W; }
+  else wrow = n0 + lr;
+  const bool wrow_ok = wrow < P.N;
+  const bool vecA = (P.lda % 4 == 0) && (aoff % 4 == 0) && (reinterpret_cast<uintptr_t>(P.A) % 16 == 0);
+  const bool vecB = (P.ldw % 8 == 0) && (woff % 8 == 0) && (reinterpret_cast<uintptr_t>(P.W) % 16 == 0) &&
+                    (!DUAL || reinterpret_cast<uintptr_t>(P.W2) % 16 == 0);
+  const int wm = warp & 1, wn = warp >> 1;
+  float acc[4][4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+#pragma unroll
+      for (int q = 0; q < 4; q++) acc[i][j][q] = 0.f;
+  for (int k0 = 0; k0 < P.K; k0 += BK) {
+    const int kb = k0 + lk;
+    {  // A: fp32 -> bf16
+      bf* dst = &As[lr][lk];
+      if (ar >= 0 && vecA && kb + 16 <= P.K) {
+        const float4* src = reinterpret_cast<const float4*>(A + (size_t)ar * P.lda + kb);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const float4 v = src[q];
+          *reinterpret_cast<__nv_bfloat162*>(dst + 4 * q) = __floats2bfloat162_rn(v.x, v.y);
+          *reinterpret_cast<__nv_bfloat162*>(dst + 4 * q + 2) = __floats2bfloat162_rn(v.z, v.w);
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 16; q++) dst[q] = __float2bfloat16_rn((ar >= 0 && kb + q < P.K) ? A[(size_t)ar * P.lda + kb + q] : 0.f);
+      }
+    }
+    {  // W: bf16 rows
+      bf* dst = &Bs[lr][lk];
+      if (wrow_ok && vecB && kb + 16 <= P.K) {
+        const uint4* src = reinterpret_cast<const uint4*>(wsrc + (size_t)wrow * P.ldw + kb);
+        *reinterpret_cast<uint4*>(dst) = src[0];
+        *reinterpret_cast<uint4*>(dst + 8) = src[1];
+      } else {
+#pragma unroll
+        for (int q = 0; q < 16; q++) dst[q] = (wrow_ok && kb + q < P.K) ? wsrc[(size_t)wrow * P.ldw + kb + q] : __float2bfloat16_rn(0.f);
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      uint32_t af[4][4], bfr[4][2];
+      const int c = kk + (lane & 3) * 2;
+#pragma unroll
+      for (int mi = 0; mi < 4; mi++) {
+        const int r = wm * 64 + mi * 16 + (lane >> 2);
+        af[mi][0] = *reinterpret_cast<const uint32_t*>(&As[r][c]);
+        af[mi][1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][c]);
+        af[mi][2] = *reinterpret_cast<const uint32_t*>(&As[r][c + 8]);
+        af[mi][3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][c + 8]);
+      }
+#pragma unroll
+      for (int ni = 0; ni < 4; ni++) {
+        const int n = wn * 32 + ni * 8 + (lane >> 2);
+        bfr[ni][0] = *reinterpret_cast<const uint32_t*>(&Bs[n][c]);
+        bfr[ni][1] = *reinterpret_cast<const uint32_t*>(&Bs[n][c + 8]);
+      }
+#pragma unroll
+      for (int mi = 0; mi < 4; mi++)
+#pragma unroll
+        for (int ni = 0; ni < 4; ni++) mma_bf16_16816(acc[mi][ni], af[mi][0], af[mi][1], af[mi][2], af[mi][3], bfr[ni][0], bfr[ni][1]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int mi = 0; mi < 4; mi++) {
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+      const int cr = rowsC[wm * 64 + mi * 16 + (lane >> 2) + half * 8];
+      if (cr < 0) continue;
+      float* crow = P.C + coff + (size_t)cr * P.ldc;
+#pragma unroll
+      for (int ni = 0; ni < 4; ni += (DUAL ? 2 : 1)) {
+#pragma unroll
+        for (int q = 0; q < 2; q++) {
+          const int g = wn * 4 + ni;   // granule of 8 staged rows
+          const int n = DUAL ? n0 + (g >> 1) * 8 + (lane & 3) * 2 + q : n0 + g * 8 + (lane & 3) * 2 + q;
+          if (n < P.N) gemm_epilogue<bf, EPI>(P, crow, cr, n, acc[mi][ni][half * 2 + q], DUAL ? acc[mi][ni + 1][half * 2 + q] : 0.f);
+        }
+      }
+    }
+  }
+}
+
 template <typename WT> struct WVec;
 template <> struct WVec<float> {
   static constexpr int N = 4;
@@ -448,12 +586,13 @@ __global__ void __launch_bounds__(512) ssd_scan(const float* __restrict__ proj, 
 // qa [T][H][R] = per-head W_uk^T q; the caller then applies the per-head value up-projection to o [T][H][R].  The latent of
 // position j is row j % ring of `cache`.  A CTA of 8 warps takes TQ consecutive tokens x 8 / TQ heads (one warp each) and walks
 // the union of their windows in tiles of 32 keys staged in shared memory, so a tile is read once per CTA; lane = key for the
-// scores, lane = latent channel (mod 32) for the weighted sum.  Online softmax in fp32.
+// scores, lane = latent channel (mod 32) for the weighted sum.  Online softmax in fp32.  With NS > 1 (few tokens: decoding) the
+// key range is cut into NS shares over blockIdx.z and latent_swa_merge combines the partial results.
 // ---------------------------------------------------------------------------------------------------------------------
 template <typename CT, int RV>
 __global__ void __launch_bounds__(256) latent_swa_attn(const float* __restrict__ qa, const CT* __restrict__ cache, float* __restrict__ out,
                                                        int T, int H, int R, const int* __restrict__ ctl, int window, int ring,
-                                                       float scale, int TQ) {
+                                                       float scale, int TQ, int NS, float* __restrict__ part) {
   extern __shared__ float sm[];
   const int NW = 8, HB = NW / TQ;
   float* qs = sm;                 // [NW][R]
@@ -465,7 +604,13 @@ __global__ void __launch_bounds__(256) latent_swa_attn(const float* __restrict__
   for (int r = lane; r < R; r += 32) qs[w * R + r] = active ? qa[((size_t)t * H + h) * R + r] * scale : 0.f;
   const int i = pos0 + t;
   const int lo_w = max(0, i - window + 1), hi_w = i;
-  const int lo = max(0, pos0 + tq0 - window + 1), hi = pos0 + min(T, tq0 + TQ) - 1;
+  int lo = max(0, pos0 + tq0 - window + 1), hi = pos0 + min(T, tq0 + TQ) - 1;
+  if (NS > 1) {   // this CTA's share of the key range (whole tiles of 32)
+    const int tiles = (hi - lo + 32) / 32, per = (tiles + NS - 1) / NS;
+    const int lo_s = lo + (int)blockIdx.z * per * 32;
+    hi = min(hi, lo_s + per * 32 - 1);
+    lo = lo_s;
+  }
   float m = -1e30f, l = 0.f, acc[RV];
 #pragma unroll
   for (int k = 0; k < RV; k++) acc[k] = 0.f;
@@ -477,7 +622,7 @@ __global__ void __launch_bounds__(256) latent_swa_attn(const float* __restrict__
     }
     __syncthreads();
     const int j = j0 + lane;
-    const bool valid = active && j >= lo_w && j <= hi_w;
+    const bool valid = active && j >= lo_w && j <= hi_w && j <= hi;
     if (!__any_sync(0xffffffffu, valid)) continue;
     float s = 0.f;
     const float* kr = ks + lane * (R + 1);
@@ -502,13 +647,38 @@ __global__ void __launch_bounds__(256) latent_swa_attn(const float* __restrict__
     }
     m = m_new;
   }
-  if (active) {
-    const float inv = 1.f / l;
+  if (!active) return;
+  if (NS > 1) {   // partial result of this key range: [t][h][split] -> {m, l, acc[R]} (not normalised); latent_swa_merge finishes
+    float* pp = part + (((size_t)t * H + h) * NS + blockIdx.z) * (R + 2);
+    if (lane == 0) { pp[0] = m; pp[1] = l; }
 #pragma unroll
     for (int k = 0; k < RV; k++) {
       const int r = lane + 32 * k;
-      if (r < R) out[((size_t)t * H + h) * R + r] = acc[k] * inv;
+      if (r < R) pp[2 + r] = acc[k];
     }
+    return;
+  }
+  const float inv = 1.f / l;
+#pragma unroll
+  for (int k = 0; k < RV; k++) {
+    const int r = lane + 32 * k;
+    if (r < R) out[((size_t)t * H + h) * R + r] = acc[k] * inv;
+  }
+}
+
+// merges the NS partial softmax results of one (token, head): out = sum_s e^(m_s - m) acc_s / sum_s e^(m_s - m) l_s
+__global__ void latent_swa_merge(const float* __restrict__ part, float* __restrict__ out, int R, int NS) {
+  const size_t th = blockIdx.x;
+  const float* pp = part + th * NS * (R + 2);
+  float m = -1e30f;
+  for (int s = 0; s < NS; s++) m = fmaxf(m, pp[(size_t)s * (R + 2)]);
+  float l = 0.f;
+  for (int s = 0; s < NS; s++) l += expf(pp[(size_t)s * (R + 2)] - m) * pp[(size_t)s * (R + 2) + 1];
+  const float inv = 1.f / l;
+  for (int r = threadIdx.x; r < R; r += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < NS; s++) a = fmaf(expf(pp[(size_t)s * (R + 2)] - m), pp[(size_t)s * (R + 2) + 2 + r], a);
+    out[th * R + r] = a * inv;
   }
 }
 

@@ -64,12 +64,15 @@ struct State {
   int *d_tok = nullptr, *d_want = nullptr, *d_ctl = nullptr, *d_idx = nullptr, *d_perm = nullptr, *d_ntiles = nullptr;
   int4* d_tiles = nullptr;
   int max_tiles = 0;
+  float* part = nullptr;                     // partial softmax results of key-split attention (decode-sized chunks)
   float *x = nullptr, *h = nullptr, *b0 = nullptr, *b1 = nullptr, *b2 = nullptr, *b3 = nullptr, *wgt = nullptr, *logits = nullptr;
   int *h_tok = nullptr, *h_want = nullptr;   // pinned staging of a chunk's token ids / wanted rows
   std::vector<void*> allocs;
   cudaGraphExec_t step_graph = nullptr;      // captured greedy decode step (arg-max -> token -> one-token chunk)
   long long launches = 0;
 };
+
+static constexpr int kAttnSplitMax = 64, kAttnSplitTokens = 4;   // decode-sized chunks split a window over up to 64 CTAs
 
 static bool is_ssd(const dsk_layer_spec& s) { return s.mixer == DSK_MIX_SSD; }
 static long long ssd_inner(const dsk_layer_spec& s) { return (long long)s.ssm_heads * s.ssm_vdim; }
@@ -412,6 +415,10 @@ static dsk_state* state_create(dsk_model* m) {
   }
   S->max_tiles = (int)(Tc * mxTop / 64 + mxE + 1);
   int rc = 0;
+  size_t mxPart = 0;
+  for (const HLayer& L : M->L)
+    if (L.sp.mixer == DSK_MIX_LATENT_SWA) mxPart = std::max(mxPart, (size_t)kAttnSplitTokens * L.sp.att_heads * kAttnSplitMax * (L.sp.att_kv_rank + 2));
+  rc |= salloc(S, (void**)&S->part, mxPart * 4);
   rc |= salloc(S, (void**)&S->x, Tc * c.dim * 4) | salloc(S, (void**)&S->h, Tc * c.dim * 4);
   rc |= salloc(S, (void**)&S->b0, Tc * mx0 * 4) | salloc(S, (void**)&S->b1, Tc * mx1 * 4) | salloc(S, (void**)&S->b2, Tc * mx2 * 4) | salloc(S, (void**)&S->b3, Tc * mx3 * 4);
   rc |= salloc(S, (void**)&S->wgt, Tc * mxTop * 4) | salloc(S, (void**)&S->d_idx, Tc * mxTop * 4) | salloc(S, (void**)&S->d_perm, Tc * mxTop * 4);
@@ -444,6 +451,17 @@ static GemmP gp(const float* A, int lda, const void* W, int ldw, float* C, int l
   return P;
 }
 
+static void launch_gemm_mma(int epi, const GemmP& P, int Z, int tile_cap, cudaStream_t st) {
+  const int bn = epi == HEPI_GLU ? 64 : 128;
+  const dim3 grid((unsigned)((P.N + bn - 1) / bn), (unsigned)(P.tiles ? tile_cap : (P.M + 127) / 128), (unsigned)Z);
+  switch (epi) {
+    case HEPI_STORE: gemm_mma<HEPI_STORE><<<grid, 256, 0, st>>>(P); break;
+    case HEPI_ADD: gemm_mma<HEPI_ADD><<<grid, 256, 0, st>>>(P); break;
+    case HEPI_GLU: gemm_mma<HEPI_GLU><<<grid, 256, 0, st>>>(P); break;
+    default: gemm_mma<HEPI_GELU_MUL><<<grid, 256, 0, st>>>(P); break;
+  }
+}
+
 template <typename WT>
 static void launch_gemm_t(int epi, const GemmP& P, int Z, bool small, int tile_cap, cudaStream_t st) {
   if (small) {
@@ -467,7 +485,8 @@ static void launch_gemm_t(int epi, const GemmP& P, int Z, bool small, int tile_c
 // C = A W^T (+ epilogue).  Z > 1: per-head batches or (gemv) one batch per routed (token, slot) pair.
 static void linear(State* S, bool bf16, int epi, const GemmP& P, int Z, cudaStream_t st, int tile_cap = 0) {
   const bool small = P.z_expert != nullptr || (!P.tiles && P.M <= 4);
-  if (bf16) launch_gemm_t<__nv_bfloat16>(epi, P, Z, small, tile_cap, st);
+  if (bf16 && !small) launch_gemm_mma(epi, P, Z, tile_cap, st);
+  else if (bf16) launch_gemm_t<__nv_bfloat16>(epi, P, Z, small, tile_cap, st);
   else launch_gemm_t<float>(epi, P, Z, small, tile_cap, st);
   S->launches++;
 }
@@ -490,14 +509,20 @@ static void launch_scan(const dsk_layer_spec& sp, const float* proj, int ld_proj
 }
 
 static void launch_attn(const float* qa, const float* cache, float* out, int T, int H, int R, const int* ctl, int window, int ring,
-                        float scale, cudaStream_t st) {
+                        float scale, float* part, cudaStream_t st) {
   const int TQ = T >= 8 ? 8 : T >= 4 ? 4 : T >= 2 ? 2 : 1, HB = 8 / TQ;
-  const dim3 grid((unsigned)((T + TQ - 1) / TQ), (unsigned)((H + HB - 1) / HB));
+  int NS = 1;
+  if (T <= kAttnSplitTokens) {   // the widest key range a CTA can meet is window + TQ - 1 keys
+    const int tiles = (std::min(window, ring) + TQ - 1 + 31) / 32;
+    NS = std::max(1, std::min(tiles, kAttnSplitMax));
+  }
+  const dim3 grid((unsigned)((T + TQ - 1) / TQ), (unsigned)((H + HB - 1) / HB), (unsigned)NS);
   const size_t smem = ((size_t)8 * R + (size_t)32 * (R + 1)) * 4;
-  if (R <= 128) latent_swa_attn<float, 4><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ);
-  else if (R <= 256) latent_swa_attn<float, 8><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ);
-  else if (R <= 512) latent_swa_attn<float, 16><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ);
-  else latent_swa_attn<float, 32><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ);
+  if (R <= 128) latent_swa_attn<float, 4><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ, NS, part);
+  else if (R <= 256) latent_swa_attn<float, 8><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ, NS, part);
+  else if (R <= 512) latent_swa_attn<float, 16><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ, NS, part);
+  else latent_swa_attn<float, 32><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ, NS, part);
+  if (NS > 1) latent_swa_merge<<<T * H, 128, 0, st>>>(part, out, R, NS);
 }
 
 // Enqueues the kernels of one chunk of T <= chunk tokens (ids in S->d_tok, first position in S->d_ctl) on `st`.
@@ -545,7 +570,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         P.sA = D; P.sW = (long long)R * D; P.sC = R;
         linear(S, bf, HEPI_STORE, P, H, st);
       }
-      launch_attn(S->b2, cache, S->b3, T, H, R, S->d_ctl, sp.att_window, O.ring, sp.att_scale, st);
+      launch_attn(S->b2, cache, S->b3, T, H, R, S->d_ctl, sp.att_window, O.ring, sp.att_scale, S->part, st);
       S->launches++;
       {  // value up-projection per head: ov[t][h][:] = W_uv[h] o[t][h][:]
         GemmP P = gp(S->b3, H * R, L.uv.p, R, S->b0, H * V, T, V, R);
@@ -570,11 +595,12 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         linear(S, bf, HEPI_GLU, G, pairs, st);
         linear(S, bf, HEPI_STORE, Dn, pairs, st);
       } else {
-        moe_plan<<<1, 256, (size_t)2 * E * 4, st>>>(S->d_idx, pairs, E, 64, S->d_perm, S->d_tiles, S->d_ntiles);
+        const int bm = bf ? 128 : 64;   // rows per tile of the product kernel that follows (gemm_mma / gemm_tiled)
+        moe_plan<<<1, 256, (size_t)2 * E * 4, st>>>(S->d_idx, pairs, E, bm, S->d_perm, S->d_tiles, S->d_ntiles);
         S->launches++;
         G.tiles = S->d_tiles; G.n_tiles = S->d_ntiles; G.a_map = S->d_perm; G.a_div = top; G.c_map = S->d_perm;
         Dn.tiles = S->d_tiles; Dn.n_tiles = S->d_ntiles; Dn.a_map = S->d_perm; Dn.a_div = 1; Dn.c_map = S->d_perm;
-        const int cap = std::min(S->max_tiles, pairs / 64 + E + 1);
+        const int cap = std::min(S->max_tiles, pairs / bm + E + 1);
         linear(S, bf, HEPI_GLU, G, 1, st, cap);
         linear(S, bf, HEPI_STORE, Dn, 1, st, cap);
       }

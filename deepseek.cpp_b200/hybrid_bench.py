@@ -1,0 +1,175 @@
+"""hybrid_bench.py — prefill and decode throughput of the layer-list family (Desarax design) at sizes that resemble a real
+model's layers, beside the closest DeepSeek model of the framework (true-MLA blocks, fp16) at equal width / depth / experts.
+
+Used by `bench.py --hybrid`.  Random weights generated on the GPU (bf16), uploaded through dsk_upload_tensor(src_on_device).
+Decode is the device-side greedy loop (CUDA events around the captured step graph); prefill is dsk_forward_chunk over a prompt
+longer than the latent window, timed by the host around the (synchronous) call after a warm-up call.  Roofline fractions are
+against the measured copy bandwidth (decode: algorithmic weight bytes per token) and the measured cuBLAS bf16 rate (prefill:
+2 x active matrix elements per token).
+"""
+import json
+import os
+import time
+
+import numpy as np
+
+SIZES = {
+    # width, vocab, layer pattern (s = state-space, a = latent attention, A = latent attention reading the previous one's cache)
+    "small": dict(width=1024, vocab=32000, pattern="ssassA", heads=32, vdim=64, state=64, groups=4, conv=4, att_heads=8, att_dim=64,
+                  att_vdim=64, kv_rank=256, window=512, experts=16, top=2, ff=512, side=32),
+    "v2lite_like": dict(width=2048, vocab=102400, pattern="ssassAssassA", heads=64, vdim=64, state=128, groups=8, conv=4, att_heads=16,
+                        att_dim=128, att_vdim=128, kv_rank=512, window=1024, experts=64, top=6, ff=1408, side=64),
+}
+
+
+def desarax_config(z):
+    layers, last_a = [], None
+    for i, ch in enumerate(z["pattern"]):
+        mlp = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"], "scale": 1.0}, "expert": {"ff": z["ff"], "limit": 7.0}}
+        if ch == "s":
+            layers.append({"type": "mamba2", "mlp": mlp, "mixer": {"heads": z["heads"], "vdim": z["vdim"], "state": z["state"], "groups": z["groups"],
+                                                                    "conv": z["conv"], "norm_groups": z["groups"]}})
+        else:
+            mx = {"heads": z["att_heads"], "dim": z["att_dim"], "vdim": z["att_vdim"], "kv_rank": z["kv_rank"], "mask": {"size": z["window"]},
+                  "scale": z["att_dim"] ** -0.5}
+            if ch == "A" and last_a is not None:
+                mx["kv_from"] = last_a
+            else:
+                last_a = i
+            layers.append({"type": "latent_attention", "mlp": mlp, "mixer": mx})
+    return {"architecture": "Desarax", "vocab": z["vocab"], "width": z["width"], "layers": layers, "norm": {"eps": 1e-5, "groups": 4},
+            "residual_mult": 0.5, "logit_scale": 1.0, "token_side": {"dim": z["side"]}}
+
+
+def mint_desarax(dsk, torch, cfg, quant, chunk, context, device=0):
+    import hashlib
+    hc, specs = dsk.hybrid_from_config(cfg, quant=quant, max_seq_len=context, chunk=chunk)
+    m = dsk.Model(hc, 0, 1, device, layers=specs)
+    dev = torch.device("cuda", device)
+    W, V, L = cfg["width"], cfg["vocab"], len(cfg["layers"])
+    sd = cfg["token_side"]["dim"]
+
+    def up(name, shape, kind="mat"):
+        torch.manual_seed(int(hashlib.md5(name.encode()).hexdigest()[:8], 16))
+        if kind == "mat":
+            t = torch.randn(*shape, device=dev) * (shape[-1] ** -0.5)
+        elif kind == "embed":
+            t = torch.randn(*shape, device=dev)
+        elif kind == "norm":
+            t = 1.0 + 0.1 * torch.randn(*shape, device=dev)
+        elif kind == "alog":
+            t = torch.log(torch.empty(*shape, device=dev).uniform_(0.5, 4.0))
+        elif kind == "dtb":
+            t = torch.empty(*shape, device=dev).uniform_(-3.0, 0.0)
+        else:
+            t = 0.1 * torch.randn(*shape, device=dev)
+        t = t.to(torch.bfloat16).contiguous()
+        m.upload_device(name, "BF16", shape, t.data_ptr(), t.numel() * 2)
+        torch.cuda.synchronize()
+
+    up("embed", (V, W), "embed"); up("final.norm", (W,), "norm"); up("side.embed", (V, sd * L), "embed")
+    for i, lc in enumerate(cfg["layers"]):
+        p, mx = f"l{i}.", lc["mixer"]
+        up(p + "norm1", (W,), "norm")
+        if "state" in mx:
+            inner, ch = mx["heads"] * mx["vdim"], mx["heads"] * mx["vdim"] + 2 * mx["groups"] * mx["state"]
+            up(p + "mix.in", (inner + ch + mx["heads"], W)); up(p + "mix.conv", (ch, mx["conv"])); up(p + "mix.conv.b", (ch,), "small")
+            up(p + "mix.dt_bias", (mx["heads"],), "dtb"); up(p + "mix.A_log", (mx["heads"],), "alog"); up(p + "mix.D", (mx["heads"],), "norm")
+            up(p + "mix.norm", (inner,), "norm"); up(p + "mix.o", (W, inner))
+        else:
+            H, D, Vd, R = mx["heads"], mx["dim"], mx["vdim"], mx["kv_rank"]
+            up(p + "mix.q", (H * D, W)); up(p + "mix.uk", (H * D, R)); up(p + "mix.uv", (H * Vd, R)); up(p + "mix.o", (W, H * Vd))
+            if "kv_from" not in mx:
+                up(p + "mix.dkv", (R, W)); up(p + "mix.dkv.norm", (R,), "norm")
+        E, ff = lc["mlp"]["router"]["experts"], lc["mlp"]["expert"]["ff"]
+        up(p + "mlp.router", (E, W)); up(p + "mlp.correction", (E,), "small")
+        for e in range(E):
+            up(f"{p}mlp.e{e}.gate", (ff, W)); up(f"{p}mlp.e{e}.up", (ff, W)); up(f"{p}mlp.e{e}.down", (W, ff))
+        up(p + "side.gate", (sd, W)); up(p + "side.proj", (W, sd)); up(p + "side.norm", (W,), "norm")
+    m.finalize()
+    return m
+
+
+def active_matrix_elements(cfg):
+    """Matrix elements one token multiplies with (for prefill FLOPs = 2 x this)."""
+    W, n = cfg["width"], cfg["width"] * cfg["vocab"]
+    for lc in cfg["layers"]:
+        mx = lc["mixer"]
+        if "state" in mx:
+            inner = mx["heads"] * mx["vdim"]
+            n += (2 * inner + 2 * mx["groups"] * mx["state"] + mx["heads"]) * W + W * inner
+        else:
+            H, D, Vd, R = mx["heads"], mx["dim"], mx["vdim"], mx["kv_rank"]
+            n += H * D * W + H * (D + Vd) * R + W * H * Vd + (0 if "kv_from" in mx else R * W)
+        n += 3 * lc["mlp"]["router"]["top"] * lc["mlp"]["expert"]["ff"] * W + lc["mlp"]["router"]["experts"] * W
+        n += 2 * cfg["token_side"]["dim"] * W
+    return n
+
+
+def peaks(repo):
+    try:
+        p = json.load(open(os.path.join(repo, "MEASURED_PEAKS.json")))
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def run(dsk, torch, repo, bench_module, sizes=("small", "v2lite_like"), prompt_len=2048, gen=128, chunk=256, log=print):
+    hbm, tfl, src = peaks(repo)
+    out = {"peaks": {"hbm_gbs": hbm, "bf16_tflops": tfl, "source": src}, "results": []}
+    for name in sizes:
+        z = SIZES[name]
+        cfg = desarax_config(z)
+        for quant in ("bf16",):
+            t0 = time.time()
+            m = mint_desarax(dsk, torch, cfg, quant, chunk, prompt_len + gen + 8)
+            log(f"hybrid/{name}/{quant}: minted {m.resident_bytes() / 1e9:.2f} GB in {time.time() - t0:.1f} s")
+            rng = np.random.RandomState(0)
+            prompt = rng.randint(0, z["vocab"], prompt_len).astype(np.int32)
+            m.forward_chunk(prompt, 0, [prompt_len - 1])                       # warm-up (also the first-use costs)
+            ts = []
+            for _ in range(3):
+                t0 = time.perf_counter()
+                m.forward_chunk(prompt, 0, [prompt_len - 1])
+                ts.append(time.perf_counter() - t0)
+            pre = prompt_len / min(ts)
+            m.decode_greedy(prompt_len, 8)                                     # captures the step graph
+            m.forward_chunk(prompt, 0, [prompt_len - 1])
+            toks, ms = m.decode_greedy(prompt_len, gen)
+            dec = gen / (ms * 1e-3)
+            ab = m.active_bytes_per_token()
+            flops = 2.0 * active_matrix_elements(cfg)
+            r = {"model": f"Desarax {name}", "quant": quant, "layers": len(cfg["layers"]), "width": z["width"], "resident_gb": m.resident_bytes() / 1e9,
+                 "prefill_tok_s": pre, "prefill_tokens": prompt_len, "chunk": chunk, "decode_tok_s": dec, "decode_tokens": gen,
+                 "active_bytes_per_token": ab, "decode_frac_of_hbm": ab * dec / (hbm * 1e9), "prefill_frac_of_bf16": flops * pre / (tfl * 1e12),
+                 "launches_per_token": m.launches_per_forward()}
+            log(json.dumps(r))
+            out["results"].append(r)
+            m.close()
+        # the closest DeepSeek model of the framework at equal width / depth / experts: true-MLA blocks, fp16 matrices
+        w = dict(bench_module.WORKLOADS["v2lite"])
+        w.update(dim=z["width"], hidden_dim=z["ff"] * z["top"], n_layers=len(z["pattern"]), n_heads=z["att_heads"], vocab_size=z["vocab"],
+                 qk_nope_head_dim=z["att_dim"], qk_rope_head_dim=64, v_head_dim=z["att_vdim"], kv_lora_rank=z["kv_rank"], q_lora_rank=z["kv_rank"],
+                 first_k_dense_replace=0, n_shared_experts=0, n_routed_experts=z["experts"], n_active_routed=z["top"], moe_intermediate_size=z["ff"],
+                 max_seq_len=1024, quant="fp16", use_mla=1)
+        t0 = time.time()
+        m = bench_module.mint_on_gpu(dsk, w, 0, 1, 0)
+        log(f"deepseek-mla/{name}/fp16: minted {m.resident_bytes() / 1e9:.2f} GB in {time.time() - t0:.1f} s")
+        n_pre = 256
+        for i in range(8):
+            m.forward(int(i), i, dsk.HYDRATE_KV_CACHE)
+        t0 = time.perf_counter()
+        for i in range(n_pre):                                                 # its prefill is the hydrate loop: one forward per token
+            m.forward(int(i % z["vocab"]), i, dsk.OUTPUT_LOGITS if i == n_pre - 1 else dsk.HYDRATE_KV_CACHE)
+        pre = n_pre / (time.perf_counter() - t0)
+        m.decode_greedy(n_pre, 8)
+        toks, ms = m.decode_greedy(n_pre + 8, gen)
+        dec = gen / (ms * 1e-3)
+        ab = m.active_bytes_per_token()
+        r = {"model": f"DeepSeek true-MLA {name}", "quant": "fp16", "layers": w["n_layers"], "width": z["width"], "resident_gb": m.resident_bytes() / 1e9,
+             "prefill_tok_s": pre, "prefill_tokens": n_pre, "decode_tok_s": dec, "decode_tokens": gen, "active_bytes_per_token": ab,
+             "decode_frac_of_hbm": ab * dec / (hbm * 1e9), "prefill_frac_of_bf16": None, "launches_per_token": m.launches_per_forward()}
+        log(json.dumps(r))
+        out["results"].append(r)
+        m.close()
+    return out
