@@ -138,6 +138,7 @@ struct GemmP {
   const int* c_map;        // logical row i writes C row c_map[i] (null: row i)
   const int* z_expert;     // gemv_rows only: batch z uses expert z_expert[z], A row z / z_adiv, C row z (one row per batch)
   int z_adiv;
+  int z_rows;              // gemv_rows only, > 0: batch z takes rows 4z .. 4z + 3 of z_rows rows (narrow outputs over many rows)
   const int4* tiles;       // gemm_tiled only: row tiles grouped by expert {expert, first logical row, rows, -}
   const int* n_tiles;
   float alpha;             // STORE: C = alpha acc; ADD: C += alpha acc
@@ -201,16 +202,27 @@ __global__ void __launch_bounds__(256) gemm_tiled(const GemmP P) {
     for (int j = 0; j < 4; j++) { acc[i][j] = 0.f; acc2[i][j] = 0.f; }
   const int ar = rowsA[lr];
   const int wn = n0 + lr;
-  for (int k0 = 0; k0 < P.K; k0 += BK) {
+  float ra[4], rb[4], rb2[4];
+  auto fetch = [&](int k0) {
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const int k = k0 + lk + j;
-      As[lk + j][lr] = (ar >= 0 && k < P.K) ? A[(size_t)ar * P.lda + k] : 0.f;
+      ra[j] = (ar >= 0 && k < P.K) ? A[(size_t)ar * P.lda + k] : 0.f;
       const bool wok = wn < P.N && k < P.K;
-      Bs[0][lk + j][lr] = wok ? to_f<WT>(W[(size_t)wn * P.ldw + k]) : 0.f;
-      if (DUAL) Bs[DUAL ? 1 : 0][lk + j][lr] = wok ? to_f<WT>(W2[(size_t)wn * P.ldw + k]) : 0.f;
+      rb[j] = wok ? to_f<WT>(W[(size_t)wn * P.ldw + k]) : 0.f;
+      rb2[j] = (DUAL && wok) ? to_f<WT>(W2[(size_t)wn * P.ldw + k]) : 0.f;
+    }
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < P.K; k0 += BK) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      As[lk + j][lr] = ra[j];
+      Bs[0][lk + j][lr] = rb[j];
+      if (DUAL) Bs[DUAL ? 1 : 0][lk + j][lr] = rb2[j];
     }
     __syncthreads();
+    if (k0 + BK < P.K) fetch(k0 + BK);   // in flight during this step's FMAs
 #pragma unroll
     for (int kk = 0; kk < BK; kk++) {
       const float4 a4 = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
@@ -306,35 +318,52 @@ __global__ void __launch_bounds__(256) gemm_mma(const GemmP P) {
     for (int j = 0; j < 4; j++)
 #pragma unroll
       for (int q = 0; q < 4; q++) acc[i][j][q] = 0.f;
-  for (int k0 = 0; k0 < P.K; k0 += BK) {
+  // the next K step's global loads are issued before the current step's tensor-core work and parked in registers
+  uint32_t ra[8], rb[8];
+  auto fetch = [&](int k0) {
     const int kb = k0 + lk;
-    {  // A: fp32 -> bf16
-      bf* dst = &As[lr][lk];
-      if (ar >= 0 && vecA && kb + 16 <= P.K) {
-        const float4* src = reinterpret_cast<const float4*>(A + (size_t)ar * P.lda + kb);
+    if (ar >= 0 && vecA && kb + 16 <= P.K) {
+      const float4* src = reinterpret_cast<const float4*>(A + (size_t)ar * P.lda + kb);
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-          const float4 v = src[q];
-          *reinterpret_cast<__nv_bfloat162*>(dst + 4 * q) = __floats2bfloat162_rn(v.x, v.y);
-          *reinterpret_cast<__nv_bfloat162*>(dst + 4 * q + 2) = __floats2bfloat162_rn(v.z, v.w);
-        }
-      } else {
+      for (int q = 0; q < 4; q++) {
+        const float4 v = src[q];
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        ra[2 * q] = *reinterpret_cast<const uint32_t*>(&lo);
+        ra[2 * q + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+      }
+    } else {
 #pragma unroll
-        for (int q = 0; q < 16; q++) dst[q] = __float2bfloat16_rn((ar >= 0 && kb + q < P.K) ? A[(size_t)ar * P.lda + kb + q] : 0.f);
+      for (int q = 0; q < 8; q++) {
+        const float v0 = (ar >= 0 && kb + 2 * q < P.K) ? A[(size_t)ar * P.lda + kb + 2 * q] : 0.f;
+        const float v1 = (ar >= 0 && kb + 2 * q + 1 < P.K) ? A[(size_t)ar * P.lda + kb + 2 * q + 1] : 0.f;
+        const __nv_bfloat162 pr = __floats2bfloat162_rn(v0, v1);
+        ra[q] = *reinterpret_cast<const uint32_t*>(&pr);
       }
     }
-    {  // W: bf16 rows
-      bf* dst = &Bs[lr][lk];
-      if (wrow_ok && vecB && kb + 16 <= P.K) {
-        const uint4* src = reinterpret_cast<const uint4*>(wsrc + (size_t)wrow * P.ldw + kb);
-        *reinterpret_cast<uint4*>(dst) = src[0];
-        *reinterpret_cast<uint4*>(dst + 8) = src[1];
-      } else {
+    if (wrow_ok && vecB && kb + 16 <= P.K) {
+      const uint4* src = reinterpret_cast<const uint4*>(wsrc + (size_t)wrow * P.ldw + kb);
+      const uint4 u0 = src[0], u1 = src[1];
+      rb[0] = u0.x; rb[1] = u0.y; rb[2] = u0.z; rb[3] = u0.w; rb[4] = u1.x; rb[5] = u1.y; rb[6] = u1.z; rb[7] = u1.w;
+    } else {
+      const unsigned short* ws = reinterpret_cast<const unsigned short*>(wsrc);
 #pragma unroll
-        for (int q = 0; q < 16; q++) dst[q] = (wrow_ok && kb + q < P.K) ? wsrc[(size_t)wrow * P.ldw + kb + q] : __float2bfloat16_rn(0.f);
+      for (int q = 0; q < 8; q++) {
+        const uint32_t v0 = (wrow_ok && kb + 2 * q < P.K) ? ws[(size_t)wrow * P.ldw + kb + 2 * q] : 0u;
+        const uint32_t v1 = (wrow_ok && kb + 2 * q + 1 < P.K) ? ws[(size_t)wrow * P.ldw + kb + 2 * q + 1] : 0u;
+        rb[q] = v0 | (v1 << 16);
       }
+    }
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < P.K; k0 += BK) {
+    {
+      uint4* da = reinterpret_cast<uint4*>(&As[lr][lk]);
+      da[0] = make_uint4(ra[0], ra[1], ra[2], ra[3]); da[1] = make_uint4(ra[4], ra[5], ra[6], ra[7]);
+      uint4* db = reinterpret_cast<uint4*>(&Bs[lr][lk]);
+      db[0] = make_uint4(rb[0], rb[1], rb[2], rb[3]); db[1] = make_uint4(rb[4], rb[5], rb[6], rb[7]);
     }
     __syncthreads();
+    if (k0 + BK < P.K) fetch(k0 + BK);
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
       uint32_t af[4][4], bfr[4][2];
@@ -408,16 +437,20 @@ __global__ void __launch_bounds__(256) gemv_rows(const GemmP P) {
     aoff = (long long)(z / P.z_adiv) * P.lda;
     coff = (long long)z * P.ldc;
     M = 1;
+  } else if (P.z_rows > 0) {
+    aoff = woff = coff = 0;
+    M = min(MR, P.z_rows - z * MR);
   } else {
     aoff = (long long)z * P.sA; woff = (long long)z * P.sW; coff = (long long)z * P.sC;
   }
+  const int mbase = P.z_rows > 0 ? z * MR : 0;
   const WT* __restrict__ W = reinterpret_cast<const WT*>(P.W) + woff;
   const WT* __restrict__ W2 = DUAL ? reinterpret_cast<const WT*>(P.W2) + woff : nullptr;
   const float* arow[MR];
   int crow_i[MR];
 #pragma unroll
   for (int m = 0; m < MR; m++) {
-    const int mm = m < M ? m : 0;
+    const int mm = mbase + (m < M ? m : 0);
     const int ar = (!P.z_expert && P.a_map) ? P.a_map[mm] / P.a_div : mm;
     arow[m] = P.A + aoff + (size_t)ar * P.lda;
     crow_i[m] = (!P.z_expert && P.c_map) ? P.c_map[mm] : mm;
@@ -504,7 +537,7 @@ __global__ void conv_history_update(const float* __restrict__ in, int ld_in, flo
 // ---------------------------------------------------------------------------------------------------------------------
 // State-space-duality recurrence over a chunk, one CTA per (head, slice of PB value channels), sequential over the tokens.
 // Thread (pl, s) owns value channel p = p0 + pl and the state entries n = s, s + 8, ... (R of them) of S[h][p][:] in registers;
-// the eight threads of a channel reduce y with shuffles.  Inputs of 16 tokens at a time are staged in shared memory.
+// the eight threads of a channel reduce y with shuffles.  Inputs of TB tokens at a time are staged in shared memory.
 //   dt = softplus(raw_dt + dt_bias_h);  S <- exp(-exp(A_log_h) dt) S + dt B x^T;  y = S^T C + D_h x;  out = y silu(z)
 // proj: the input projection's rows [z | . | . | . | raw dt]; xbc: the convolved [x | B | C] rows.  Head h reads B/C group h / (H / G).
 // ---------------------------------------------------------------------------------------------------------------------
@@ -513,8 +546,7 @@ __global__ void __launch_bounds__(512) ssd_scan(const float* __restrict__ proj, 
                                                 const float* __restrict__ xbc, int ld_xbc, int x_off, int b_off, int c_off,
                                                 const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                                                 const float* __restrict__ Dskip, float* __restrict__ state,
-                                                float* __restrict__ out, int ld_out, int T, int H, int P, int N, int G, int PB) {
-  constexpr int TB = 16;
+                                                float* __restrict__ out, int ld_out, int T, int H, int P, int N, int G, int PB, int TB) {
   extern __shared__ float sm[];
   float* s_dt = sm;                 // [TB]
   float* s_dA = s_dt + TB;          // [TB]
@@ -624,10 +656,16 @@ __global__ void __launch_bounds__(256) latent_swa_attn(const float* __restrict__
     const int j = j0 + lane;
     const bool valid = active && j >= lo_w && j <= hi_w && j <= hi;
     if (!__any_sync(0xffffffffu, valid)) continue;
-    float s = 0.f;
     const float* kr = ks + lane * (R + 1);
     const float* qr = qs + w * R;
-    for (int r = 0; r < R; r++) s = fmaf(qr[r], kr[r], s);
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;   // four chains: the dot product is latency-bound otherwise
+    int r = 0;
+    for (; r + 4 <= R; r += 4) {
+      s0 = fmaf(qr[r], kr[r], s0); s1 = fmaf(qr[r + 1], kr[r + 1], s1);
+      s2 = fmaf(qr[r + 2], kr[r + 2], s2); s3 = fmaf(qr[r + 3], kr[r + 3], s3);
+    }
+    for (; r < R; r++) s0 = fmaf(qr[r], kr[r], s0);
+    float s = (s0 + s1) + (s2 + s3);
     s = valid ? s : -1e30f;
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);

@@ -64,6 +64,7 @@ struct State {
   int *d_tok = nullptr, *d_want = nullptr, *d_ctl = nullptr, *d_idx = nullptr, *d_perm = nullptr, *d_ntiles = nullptr;
   int4* d_tiles = nullptr;
   int max_tiles = 0;
+  int head_rows = 0;                         // rows of the logits buffer: the LM head runs over the wanted rows in groups of this size
   float* part = nullptr;                     // partial softmax results of key-split attention (decode-sized chunks)
   float *x = nullptr, *h = nullptr, *b0 = nullptr, *b1 = nullptr, *b2 = nullptr, *b3 = nullptr, *wgt = nullptr, *logits = nullptr;
   int *h_tok = nullptr, *h_want = nullptr;   // pinned staging of a chunk's token ids / wanted rows
@@ -119,6 +120,11 @@ static void set_kernel_attrs() {
   cudaFuncSetAttribute(latent_swa_attn<float, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   cudaFuncSetAttribute(latent_swa_attn<float, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   cudaFuncSetAttribute(latent_swa_attn<float, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(ssd_scan<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(ssd_scan<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(ssd_scan<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(ssd_scan<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(ssd_scan<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(ssd_scan<12>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(ssd_scan<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(ssd_scan<24>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(ssd_scan<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   done = true;
 }
 
@@ -424,7 +430,8 @@ static dsk_state* state_create(dsk_model* m) {
   rc |= salloc(S, (void**)&S->wgt, Tc * mxTop * 4) | salloc(S, (void**)&S->d_idx, Tc * mxTop * 4) | salloc(S, (void**)&S->d_perm, Tc * mxTop * 4);
   rc |= salloc(S, (void**)&S->d_tiles, (size_t)S->max_tiles * sizeof(int4)) | salloc(S, (void**)&S->d_ntiles, 16);
   rc |= salloc(S, (void**)&S->d_tok, Tc * 4) | salloc(S, (void**)&S->d_want, Tc * 4) | salloc(S, (void**)&S->d_ctl, 16);
-  rc |= salloc(S, (void**)&S->logits, Tc * (size_t)c.vocab_size * 4);
+  S->head_rows = (int)std::min<size_t>(Tc, 256);
+  rc |= salloc(S, (void**)&S->logits, (size_t)S->head_rows * c.vocab_size * 4);
   if (rc) { fail(-2, "state allocation failed"); return nullptr; }
   if (cudaMallocHost((void**)&S->h_tok, Tc * 4) != cudaSuccess || cudaMallocHost((void**)&S->h_want, Tc * 4) != cudaSuccess) { fail(-2, "pinned allocation failed"); return nullptr; }
   m->n_states++;
@@ -485,6 +492,15 @@ static void launch_gemm_t(int epi, const GemmP& P, int Z, bool small, int tile_c
 // C = A W^T (+ epilogue).  Z > 1: per-head batches or (gemv) one batch per routed (token, slot) pair.
 static void linear(State* S, bool bf16, int epi, const GemmP& P, int Z, cudaStream_t st, int tile_cap = 0) {
   const bool small = P.z_expert != nullptr || (!P.tiles && P.M <= 4);
+  if (!small && !P.tiles && Z == 1 && P.N <= 64) {   // narrow output (router, token-input gate): warp-per-row products over batches of 4 rows
+    GemmP Q = P;
+    Q.z_rows = P.M;
+    const int zb = (P.M + 3) / 4;
+    if (bf16) launch_gemm_t<__nv_bfloat16>(epi, Q, zb, true, 0, st);
+    else launch_gemm_t<float>(epi, Q, zb, true, 0, st);
+    S->launches++;
+    return;
+  }
   if (bf16 && !small) launch_gemm_mma(epi, P, Z, tile_cap, st);
   else if (bf16) launch_gemm_t<__nv_bfloat16>(epi, P, Z, small, tile_cap, st);
   else launch_gemm_t<float>(epi, P, Z, small, tile_cap, st);
@@ -498,10 +514,11 @@ static void launch_scan(const dsk_layer_spec& sp, const float* proj, int ld_proj
   const int PB = std::min(P, 64);
   const dim3 grid((unsigned)H, (unsigned)((P + PB - 1) / PB));
   const int threads = ((PB * 8 + 31) / 32) * 32;
-  const size_t smem = (size_t)16 * (2 + 2 * N + 2 * PB) * 4;
+  const int TB = T >= 64 ? 64 : 16;   // tokens staged per round
+  const size_t smem = (size_t)TB * (2 + 2 * N + 2 * PB) * 4;
   const int need = (N + 7) / 8;
 #define DSK_SCAN(R) ssd_scan<R><<<grid, threads, smem, st>>>(proj, ld_proj, 0, inner + (int)ssd_channels(sp), xbc, ld_xbc, 0, inner, inner + G * N, \
-                                                             L.dt_bias, L.A_log, L.D, state, out, inner, T, H, P, N, G, PB)
+                                                             L.dt_bias, L.A_log, L.D, state, out, inner, T, H, P, N, G, PB, TB)
   if (need <= 1) DSK_SCAN(1); else if (need <= 2) DSK_SCAN(2); else if (need <= 4) DSK_SCAN(4); else if (need <= 6) DSK_SCAN(6);
   else if (need <= 8) DSK_SCAN(8); else if (need <= 12) DSK_SCAN(12); else if (need <= 16) DSK_SCAN(16); else if (need <= 24) DSK_SCAN(24);
   else DSK_SCAN(32);
@@ -523,6 +540,16 @@ static void launch_attn(const float* qa, const float* cache, float* out, int T, 
   else if (R <= 512) latent_swa_attn<float, 16><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ, NS, part);
   else latent_swa_attn<float, 32><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ, NS, part);
   if (NS > 1) latent_swa_merge<<<T * H, 128, 0, st>>>(part, out, R, NS);
+}
+
+// LM head on the wanted rows [first, first + count) of the chunk whose normalised rows are in S->h -> S->logits [count][vocab]
+static void enqueue_head(dsk_model* m, dsk_state* s, int first, int count, cudaStream_t st) {
+  Model* M = m->hy;
+  State* S = s->hy;
+  const dsk_hybrid_config& c = M->c;
+  GemmP P = gp(S->h, c.dim, M->embed.p, c.dim, S->logits, c.vocab_size, count, c.vocab_size, c.dim);
+  P.a_map = S->d_want + first; P.alpha = c.logit_scale;
+  linear(S, c.quant == DSK_BF16, HEPI_STORE, P, 1, st);
 }
 
 // Enqueues the kernels of one chunk of T <= chunk tokens (ids in S->d_tok, first position in S->d_ctl) on `st`.
@@ -618,12 +645,10 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
     }
     if (trace) CKL(cudaMemcpyAsync(trace + (size_t)li * T * W, S->x, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st));
   }
-  if (n_want > 0) {
+  if (n_want > 0) {   // final norm of every row, LM head on the first group of wanted rows (enqueue_head does the others)
     group_rmsnorm<float><<<T, 256, 0, st>>>(S->x, W, M->final_norm, S->h, W, W, c.norm_groups, c.norm_eps, 0, 0.f, nullptr, 0);
-    GemmP P = gp(S->h, W, M->embed.p, W, S->logits, c.vocab_size, n_want, c.vocab_size, W);
-    P.a_map = S->d_want; P.alpha = c.logit_scale;
-    linear(S, bf, HEPI_STORE, P, 1, st);
     S->launches++;
+    enqueue_head(m, s, 0, std::min(n_want, S->head_rows), st);
   }
   CKL(cudaGetLastError());
   return 0;
@@ -657,9 +682,13 @@ static int forward_chunk(dsk_model* m, dsk_state* s, const int32_t* tokens, int 
     set_ctl<<<1, 1, 0, s->stream>>>(S->d_ctl, pos0 + o);
     if (host_layers) { CK(cudaMalloc((void**)&d_trace, (size_t)c.n_layers * T * c.dim * 4)); }
     if (enqueue_chunk(m, s, T, nw, d_trace, s->stream)) { if (d_trace) cudaFree(d_trace); return -2; }
-    if (nw && host_logits) CK(cudaMemcpyAsync(host_logits + (size_t)wi * c.vocab_size, S->logits, (size_t)nw * c.vocab_size * 4, cudaMemcpyDeviceToHost, s->stream));
+    for (int g0 = 0; g0 < nw; g0 += S->head_rows) {   // the LM head in groups of head_rows wanted rows
+      const int gn = std::min(S->head_rows, nw - g0);
+      if (g0 > 0) enqueue_head(m, s, g0, gn, s->stream);
+      if (host_logits) CK(cudaMemcpyAsync(host_logits + (size_t)(wi + g0) * c.vocab_size, S->logits, (size_t)gn * c.vocab_size * 4, cudaMemcpyDeviceToHost, s->stream));
+    }
     if (nw) {   // the last wanted row stays in the state for the samplers
-      CK(cudaMemcpyAsync(s->logits, S->logits + (size_t)(nw - 1) * c.vocab_size, (size_t)c.vocab_size * 4, cudaMemcpyDeviceToDevice, s->stream));
+      CK(cudaMemcpyAsync(s->logits, S->logits + (size_t)((nw - 1) % S->head_rows) * c.vocab_size, (size_t)c.vocab_size * 4, cudaMemcpyDeviceToDevice, s->stream));
       argmax_row<<<1, 1024, 0, s->stream>>>(s->logits, c.vocab_size, s->ctrl, nullptr, nullptr, 0);
     }
     if (host_layers) {

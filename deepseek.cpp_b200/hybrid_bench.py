@@ -114,7 +114,7 @@ def peaks(repo):
         return 6650.0, 1590.0, "fallback"
 
 
-def run(dsk, torch, repo, bench_module, sizes=("small", "v2lite_like"), prompt_len=2048, gen=128, chunk=256, log=print):
+def run(dsk, torch, repo, bench_module, sizes=("small", "v2lite_like"), prompt_len=2048, gen=128, chunk=2048, log=print):
     hbm, tfl, src = peaks(repo)
     out = {"peaks": {"hbm_gbs": hbm, "bf16_tflops": tfl, "source": src}, "results": []}
     for name in sizes:

@@ -17,6 +17,13 @@ def rel(a, b):
     return float(np.abs(np.asarray(a, np.float64) - b).max() / max(np.abs(b).max(), 1e-30))
 
 
+def close_bf16(a, b):
+    """bfloat16 products against the float64 oracle, row by row: rounding errors are about 1e-3 of the scale for most rows and
+    several times that where a small norm or a sharp softmax magnifies them; a wrong kernel is off by O(1) everywhere."""
+    e = np.abs(np.asarray(a, np.float64) - b).max(-1) / max(np.abs(b).max(), 1e-30)
+    return float(np.median(e)) < 1e-2 and float(np.quantile(e, 0.95)) < 3e-2 and float(e.max()) < 0.25
+
+
 @pytest.fixture(scope="module")
 def ho():
     import hybrid_oracle
@@ -284,14 +291,27 @@ def test_other_sizes(mk, ho, case):
     assert rel(np.concatenate(rows), exp) < F32_TOL
 
 
+def test_large_steps_and_many_wanted_rows(mk, ho):
+    """A step size above 256 with every row wanted: the LM head runs over the wanted rows in several groups, the routed
+    feed-forward sees full row tiles, the scan stages 64 tokens per round."""
+    cfg = model_cfg([ssd_layer(mlp=moe(E=3, top=2)), att_layer(win=50)], side=4)
+    toks = tokens_for(cfg, 330, 7)
+    for quant in ("fp32", "bf16"):
+        m, W = mk(cfg, seed=41, chunk=512, quant=quant)
+        exp = ho.run(cfg, W, toks)[0]
+        ok = (lambda a, b: rel(a, b) < F32_TOL) if quant == "fp32" else close_bf16
+        assert ok(m.forward_chunk(toks, 0, range(330)), exp)
+        assert ok(m.forward_chunk(toks[:300], 0, [0, 150, 299]), exp[[0, 150, 299]])
+
+
 def test_bf16_matrices(mk, ho):
     cfg = ho.small_config()
     m, W = mk(cfg, seed=11, quant="bf16", chunk=8)
     toks = tokens_for(cfg, 50, 4)
     exp = ho.run(cfg, W, toks)[0]
-    assert rel(m.forward_chunk(toks, 0, range(50)), exp) < BF16_TOL
+    assert close_bf16(m.forward_chunk(toks, 0, range(50)), exp)
     rows = [m.forward_chunk(toks[:30], 0, range(30))] + [m.forward_chunk(toks[i:i + 1], i, [0]) for i in range(30, 50)]
-    assert rel(np.concatenate(rows), exp) < BF16_TOL
+    assert close_bf16(np.concatenate(rows), exp)
 
 
 # ---- generation through the framework's own entry points -------------------------------------------------------------------------
