@@ -721,6 +721,53 @@ __global__ void latent_swa_merge(const float* __restrict__ part, float* __restri
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
+// Large portions (prefill) run the same attention as three matrix products per block of queries instead: keys and values of the
+// visible positions are up-projected from the cached latents (k = W_uk c, v = W_uv c), scores = q k^T per head, a banded softmax,
+// then probabilities x values.  The helpers: the ring rows of a run of positions, the per-head repacking of the up-projected
+// keys ([head][key][dim]) and values ([head][vdim][key], i.e. transposed, so that both serve as the [N][K] operand of the
+// product kernels), and the softmax over the band 0 <= i - j < window of a [head][query][key] score array.
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void ring_rows(int first, int n, int ring, int* __restrict__ rows) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) rows[i] = (first + i) % ring;
+}
+
+template <typename WT>
+__global__ void pack_keys_values(const float* __restrict__ kf, const float* __restrict__ vf, WT* __restrict__ kb, WT* __restrict__ vt,
+                                 int Lk, int H, int D, int V) {
+  const int j = blockIdx.x;
+  for (int e = threadIdx.x; e < H * D; e += blockDim.x) {
+    const int h = e / D, d = e - h * D;
+    kb[((size_t)h * Lk + j) * D + d] = from_f<WT>(kf[(size_t)j * H * D + e]);
+  }
+  for (int e = threadIdx.x; e < H * V; e += blockDim.x) {
+    const int h = e / V, v = e - h * V;
+    vt[((size_t)h * V + v) * Lk + j] = from_f<WT>(vf[(size_t)j * H * V + e]);
+  }
+}
+
+// S [H][Tq][Lk] in place: column c is position first + c, row t is position qpos0 + t; entries outside the window become 0
+__global__ void __launch_bounds__(128) softmax_band(float* __restrict__ S, int Tq, int Lk, int first, int qpos0, int window) {
+  __shared__ float red[33];
+  const int t = blockIdx.x, h = blockIdx.y;
+  float* row = S + ((size_t)h * Tq + t) * Lk;
+  const int i = qpos0 + t;
+  const int c_lo = max(0, i - window + 1 - first), c_hi = i - first;   // inclusive
+  float mx = -1e30f;
+  for (int c = c_lo + (int)threadIdx.x; c <= c_hi; c += blockDim.x) mx = fmaxf(mx, row[c]);
+  mx = warp_max(mx);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  float sum = 0.f;
+  for (int c = c_lo + (int)threadIdx.x; c <= c_hi; c += blockDim.x) { const float p = expf(row[c] - mx); row[c] = p; sum += p; }
+  sum = block_sum(sum, red);
+  const float inv = 1.f / sum;
+  for (int c = threadIdx.x; c < Lk; c += blockDim.x) row[c] = (c >= c_lo && c <= c_hi) ? row[c] * inv : 0.f;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
 // Router of a routed feed-forward, one CTA per token.  s = sigmoid(logits); the `top` experts with the largest s + correction
 // are taken (ties: lower index first), slot = rank; weights = s / (sum of the chosen s + 1e-20) * scale.
 // ---------------------------------------------------------------------------------------------------------------------

@@ -29,7 +29,8 @@ struct HLayer {
   HTensor in, o;
   float *conv_w = nullptr, *conv_b = nullptr, *dt_bias = nullptr, *A_log = nullptr, *D = nullptr, *mnorm = nullptr;
   // latent attention
-  HTensor q, dkv, ukT, uv;          // ukT: [heads][kv_rank][dim], the transposed key up-projection (absorbed into the query)
+  HTensor q, dkv, ukT, uk, uv;      // ukT: [heads][kv_rank][dim], the transposed key up-projection (absorbed into the query);
+                                    // uk: the same matrix as stored, for portions that up-project the keys instead
   float* dkv_norm = nullptr;
   int owner = -1;                   // layer whose latent cache this layer reads (itself unless kv_from)
   int ring = 0;                     // rows of this layer's own ring cache (owners only)
@@ -66,6 +67,11 @@ struct State {
   int max_tiles = 0;
   int head_rows = 0;                         // rows of the logits buffer: the LM head runs over the wanted rows in groups of this size
   float* part = nullptr;                     // partial softmax results of key-split attention (decode-sized chunks)
+  // prefill attention as matrix products (blocks of kPrefillQ queries): up-projected keys / values, their per-head packing, scores
+  float *kf = nullptr, *vf = nullptr, *sc = nullptr;
+  void *kb = nullptr, *vt = nullptr;
+  int* d_rows = nullptr;
+  int prefill_keys = 0;                      // keys a block of queries can see at most; 0: the matrix path is off
   float *x = nullptr, *h = nullptr, *b0 = nullptr, *b1 = nullptr, *b2 = nullptr, *b3 = nullptr, *wgt = nullptr, *logits = nullptr;
   int *h_tok = nullptr, *h_want = nullptr;   // pinned staging of a chunk's token ids / wanted rows
   std::vector<void*> allocs;
@@ -73,6 +79,7 @@ struct State {
   long long launches = 0;
 };
 
+static constexpr int kPrefillQ = 256, kPrefillMin = 32;   // prefill attention: queries per block / smallest portion that takes the matrix path
 static constexpr int kAttnSplitMax = 64, kAttnSplitTokens = 4;   // decode-sized chunks split a window over up to 64 CTAs
 
 static bool is_ssd(const dsk_layer_spec& s) { return s.mixer == DSK_MIX_SSD; }
@@ -241,7 +248,7 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
     } else {
       const long long H = s.att_heads;
       if (k == "q") return MAT(L.q, H * s.att_dim, c.dim);
-      if (k == "uk") return MAT(L.ukT, H * s.att_dim, s.att_kv_rank, s.att_dim);
+      if (k == "uk") { if (int rc = MAT(L.ukT, H * s.att_dim, s.att_kv_rank, s.att_dim)) return rc; return MAT(L.uk, H * s.att_dim, s.att_kv_rank); }
       if (k == "uv") return MAT(L.uv, H * s.att_vdim, s.att_kv_rank);
       if (k == "o") return MAT(L.o, c.dim, H * s.att_vdim);
       if (s.att_kv_from < 0) {
@@ -299,7 +306,7 @@ static int finalize(dsk_model* m) {
       if (!L.in.present || !L.o.present || !L.conv_w || !L.conv_b || !L.dt_bias || !L.A_log || !L.D || !L.mnorm)
         return fail(-5, "layer %d: missing state-space mixer tensors (mix.in, conv, conv.b, dt_bias, A_log, D, norm, o)", i);
     } else {
-      if (!L.q.present || !L.ukT.present || !L.uv.present || !L.o.present) return fail(-5, "layer %d: missing latent-attention tensors (mix.q, uk, uv, o)", i);
+      if (!L.q.present || !L.ukT.present || !L.uk.present || !L.uv.present || !L.o.present) return fail(-5, "layer %d: missing latent-attention tensors (mix.q, uk, uv, o)", i);
       if (s.att_kv_from < 0 && (!L.dkv.present || !L.dkv_norm)) return fail(-5, "layer %d: missing mix.dkv / mix.dkv.norm", i);
     }
     if (s.ff_kind == DSK_FF_MOE) {
@@ -410,7 +417,8 @@ static dsk_state* state_create(dsk_model* m) {
       }
       mx0 = std::max<size_t>(mx0, std::max((size_t)sp.att_heads * sp.att_dim, (size_t)sp.att_heads * sp.att_vdim));
       mx1 = std::max<size_t>(mx1, sp.att_kv_rank);
-      mx2 = std::max<size_t>(mx2, (size_t)sp.att_heads * sp.att_kv_rank); mx3 = std::max<size_t>(mx3, (size_t)sp.att_heads * sp.att_kv_rank);
+      mx2 = std::max<size_t>(mx2, (size_t)sp.att_heads * sp.att_kv_rank);
+      mx3 = std::max<size_t>(mx3, std::max((size_t)sp.att_heads * sp.att_kv_rank, (size_t)sp.att_heads * sp.att_vdim));
     }
     if (sp.ff_kind == DSK_FF_MOE) {
       mxE = std::max<size_t>(mxE, sp.ff_experts); mxTop = std::max<size_t>(mxTop, sp.ff_top);
@@ -425,6 +433,22 @@ static dsk_state* state_create(dsk_model* m) {
   for (const HLayer& L : M->L)
     if (L.sp.mixer == DSK_MIX_LATENT_SWA) mxPart = std::max(mxPart, (size_t)kAttnSplitTokens * L.sp.att_heads * kAttnSplitMax * (L.sp.att_kv_rank + 2));
   rc |= salloc(S, (void**)&S->part, mxPart * 4);
+  if ((int)Tc >= kPrefillMin) {   // buffers of the matrix-product attention path, unless a window is too long for them
+    size_t keys = 0, hd = 0, hv = 0, heads = 0;
+    for (const HLayer& L : M->L) {
+      if (L.sp.mixer != DSK_MIX_LATENT_SWA) continue;
+      keys = std::max<size_t>(keys, (size_t)std::min<long long>((long long)L.sp.att_window - 1, (long long)c.max_seq_len) + std::min<size_t>(Tc, kPrefillQ));
+      hd = std::max<size_t>(hd, (size_t)L.sp.att_heads * L.sp.att_dim); hv = std::max<size_t>(hv, (size_t)L.sp.att_heads * L.sp.att_vdim);
+      heads = std::max<size_t>(heads, L.sp.att_heads);
+    }
+    const size_t bytes = keys * (hd + hv) * (4 + M->wsize) + heads * kPrefillQ * keys * 4;
+    if (keys > 0 && bytes <= ((size_t)4 << 30)) {
+      S->prefill_keys = (int)keys;
+      rc |= salloc(S, (void**)&S->kf, keys * hd * 4) | salloc(S, (void**)&S->vf, keys * hv * 4);
+      rc |= salloc(S, &S->kb, keys * hd * M->wsize) | salloc(S, &S->vt, keys * hv * M->wsize);
+      rc |= salloc(S, (void**)&S->sc, heads * kPrefillQ * keys * 4) | salloc(S, (void**)&S->d_rows, keys * 4);
+    }
+  }
   rc |= salloc(S, (void**)&S->x, Tc * c.dim * 4) | salloc(S, (void**)&S->h, Tc * c.dim * 4);
   rc |= salloc(S, (void**)&S->b0, Tc * mx0 * 4) | salloc(S, (void**)&S->b1, Tc * mx1 * 4) | salloc(S, (void**)&S->b2, Tc * mx2 * 4) | salloc(S, (void**)&S->b3, Tc * mx3 * 4);
   rc |= salloc(S, (void**)&S->wgt, Tc * mxTop * 4) | salloc(S, (void**)&S->d_idx, Tc * mxTop * 4) | salloc(S, (void**)&S->d_perm, Tc * mxTop * 4);
@@ -555,7 +579,9 @@ static void enqueue_head(dsk_model* m, dsk_state* s, int first, int count, cudaS
 // Enqueues the kernels of one chunk of T <= chunk tokens (ids in S->d_tok, first position in S->d_ctl) on `st`.
 // n_want > 0: the LM head runs on the rows listed in S->d_want -> S->logits [n_want][vocab].  trace (device, nullable):
 // [layers][T][width] copies of the residual stream after every layer.
-static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* trace, cudaStream_t st) {
+// pos0 >= 0: the first position as the host knows it (portions may then take the matrix-product attention path); -1 inside a
+// captured step, where positions live in device memory only.
+static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* trace, cudaStream_t st, int pos0 = -1) {
   Model* M = m->hy;
   State* S = s->hy;
   const dsk_hybrid_config& c = M->c;
@@ -592,19 +618,46 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         group_rmsnorm<float><<<T, 256, 0, st>>>(S->b1, R, L.dkv_norm, cache, R, R, 1, c.norm_eps, 0, 0.f, S->d_ctl, O.ring);
         S->launches++;
       }
-      {  // absorbed query: qa[t][h][:] = W_uk[h]^T q[t][h][:]
-        GemmP P = gp(S->b0, H * D, L.ukT.p, D, S->b2, H * R, T, R, D);
-        P.sA = D; P.sW = (long long)R * D; P.sC = R;
-        linear(S, bf, HEPI_STORE, P, H, st);
+      const float* ov = S->b0;   // [T][H*V] heads' outputs
+      if (pos0 >= 0 && T >= kPrefillMin && S->prefill_keys > 0) {
+        // a portion: blocks of kPrefillQ queries, each as  k, v = up-projections of the visible latents;  P = softmax_band(q k^T);  o = P v
+        ov = S->b3;
+        for (int t0 = 0; t0 < T; t0 += kPrefillQ) {
+          const int Tq = std::min(kPrefillQ, T - t0), qpos0 = pos0 + t0;
+          const int first = std::max(0, qpos0 - sp.att_window + 1), Lk = qpos0 + Tq - first;
+          ring_rows<<<(Lk + 255) / 256, 256, 0, st>>>(first, Lk, O.ring, S->d_rows);
+          GemmP K = gp(cache, R, L.uk.p, R, S->kf, H * D, Lk, H * D, R);
+          K.a_map = S->d_rows;
+          linear(S, bf, HEPI_STORE, K, 1, st);
+          GemmP Vp = gp(cache, R, L.uv.p, R, S->vf, H * V, Lk, H * V, R);
+          Vp.a_map = S->d_rows;
+          linear(S, bf, HEPI_STORE, Vp, 1, st);
+          if (bf) pack_keys_values<__nv_bfloat16><<<Lk, 256, 0, st>>>(S->kf, S->vf, (__nv_bfloat16*)S->kb, (__nv_bfloat16*)S->vt, Lk, H, D, V);
+          else pack_keys_values<float><<<Lk, 256, 0, st>>>(S->kf, S->vf, (float*)S->kb, (float*)S->vt, Lk, H, D, V);
+          GemmP Sc = gp(S->b0 + (size_t)t0 * H * D, H * D, S->kb, D, S->sc, Lk, Tq, Lk, D);
+          Sc.sA = D; Sc.sW = (long long)Lk * D; Sc.sC = (long long)Tq * Lk; Sc.alpha = sp.att_scale;
+          linear(S, bf, HEPI_STORE, Sc, H, st);
+          softmax_band<<<dim3((unsigned)Tq, (unsigned)H), 128, 0, st>>>(S->sc, Tq, Lk, first, qpos0, sp.att_window);
+          GemmP Ov = gp(S->sc, Lk, S->vt, Lk, S->b3 + (size_t)t0 * H * V, H * V, Tq, V, Lk);
+          Ov.sA = (long long)Tq * Lk; Ov.sW = (long long)V * Lk; Ov.sC = V;
+          linear(S, bf, HEPI_STORE, Ov, H, st);
+          S->launches += 3;
+        }
+      } else {
+        {  // absorbed query: qa[t][h][:] = W_uk[h]^T q[t][h][:]
+          GemmP P = gp(S->b0, H * D, L.ukT.p, D, S->b2, H * R, T, R, D);
+          P.sA = D; P.sW = (long long)R * D; P.sC = R;
+          linear(S, bf, HEPI_STORE, P, H, st);
+        }
+        launch_attn(S->b2, cache, S->b3, T, H, R, S->d_ctl, sp.att_window, O.ring, sp.att_scale, S->part, st);
+        S->launches++;
+        {  // value up-projection per head: ov[t][h][:] = W_uv[h] o[t][h][:]
+          GemmP P = gp(S->b3, H * R, L.uv.p, R, S->b0, H * V, T, V, R);
+          P.sA = R; P.sW = (long long)V * R; P.sC = V;
+          linear(S, bf, HEPI_STORE, P, H, st);
+        }
       }
-      launch_attn(S->b2, cache, S->b3, T, H, R, S->d_ctl, sp.att_window, O.ring, sp.att_scale, S->part, st);
-      S->launches++;
-      {  // value up-projection per head: ov[t][h][:] = W_uv[h] o[t][h][:]
-        GemmP P = gp(S->b3, H * R, L.uv.p, R, S->b0, H * V, T, V, R);
-        P.sA = R; P.sW = (long long)V * R; P.sC = V;
-        linear(S, bf, HEPI_STORE, P, H, st);
-      }
-      GemmP P = gp(S->b0, H * V, L.o.p, H * V, S->x, W, T, W, H * V);
+      GemmP P = gp(ov, H * V, L.o.p, H * V, S->x, W, T, W, H * V);
       P.alpha = mult;
       linear(S, bf, HEPI_ADD, P, 1, st);
     }
@@ -681,7 +734,7 @@ static int forward_chunk(dsk_model* m, dsk_state* s, const int32_t* tokens, int 
     if (nw) CK(cudaMemcpyAsync(S->d_want, S->h_want, (size_t)nw * 4, cudaMemcpyHostToDevice, s->stream));
     set_ctl<<<1, 1, 0, s->stream>>>(S->d_ctl, pos0 + o);
     if (host_layers) { CK(cudaMalloc((void**)&d_trace, (size_t)c.n_layers * T * c.dim * 4)); }
-    if (enqueue_chunk(m, s, T, nw, d_trace, s->stream)) { if (d_trace) cudaFree(d_trace); return -2; }
+    if (enqueue_chunk(m, s, T, nw, d_trace, s->stream, pos0 + o)) { if (d_trace) cudaFree(d_trace); return -2; }
     for (int g0 = 0; g0 < nw; g0 += S->head_rows) {   // the LM head in groups of head_rows wanted rows
       const int gn = std::min(S->head_rows, nw - g0);
       if (g0 > 0) enqueue_head(m, s, g0, gn, s->stream);

@@ -203,12 +203,13 @@ def peaky(W):
             W[k] *= 3.0          # scores x 9: the softmax is dominated by a few keys, so a wrong edge moves the output by O(1)
 
 
+@pytest.mark.parametrize("chunk", [8, 64])     # small steps: the absorbed-query kernel; steps of 32 tokens and more: the matrix-product path
 @pytest.mark.parametrize("win", [1, 2, 5, 16])
-def test_window_edge_sensitivity(mk, win):
+def test_window_edge_sensitivity(mk, win, chunk):
     """One attention layer, no recurrence: the logits at position i depend on exactly the tokens i - win + 1 .. i.  Changing the
     token just outside the window must change nothing, the one just inside must change the result; in prompts and in decoding."""
     cfg = model_cfg([att_layer(heads=2, win=win, rank=12)], groups=1)
-    m, W = mk(cfg, seed=21, chunk=8)         # plain random weights: every key of the window carries a visible share
+    m, W = mk(cfg, seed=21, chunk=chunk)     # plain random weights: every key of the window carries a visible share
     n = 40
     base = tokens_for(cfg, n, 5)
     i = n - 1
@@ -230,13 +231,14 @@ def test_window_edge_sensitivity(mk, win):
         assert np.abs(last_logits(inside, decode) - ref).max() > 1e-3
 
 
-def test_window_edges_and_far_key_vs_oracle(mk, ho):
+@pytest.mark.parametrize("chunk", [8, 64])
+def test_window_edges_and_far_key_vs_oracle(mk, ho, chunk):
     """Peaky attention (scores x 9: one or two keys take nearly all the weight, wherever in the window they sit) over windows of
     23 and 150 tokens, the second reading the first one's latents, with a small step size: dominant keys fall on every offset to
     step, ring and window borders, far back and next to the edge.  Prompt in uneven portions, then decoding."""
     cfg = model_cfg([att_layer(heads=3, win=23, rank=16), ssd_layer(), att_layer(heads=2, dim=6, vdim=7, rank=16, win=150, scale=0.4, src=0)], groups=1)
 
-    m, W = mk(cfg, seed=23, chunk=8, edit=peaky)
+    m, W = mk(cfg, seed=23, chunk=chunk, edit=peaky)
     n = 200
     toks = tokens_for(cfg, n, 6)
     exp = ho.run(cfg, W, toks)[0]
