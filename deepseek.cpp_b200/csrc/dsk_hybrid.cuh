@@ -9,8 +9,8 @@
 //                     scaled, into the residual, or write its rows into a ring cache
 //   gemm_tiled        C = A W^T for T > 4 rows (fp32 activations, fp32 or bf16 weights, fp32 accumulate) with fused
 //                     epilogues (residual add, clamped GLU, GELU x per-token embedding) and row gather / scatter / expert tiles
-//   gemm_mma          the same contract on the tensor cores for bf16 weights (activations rounded to bf16 as they are staged)
-//   gemv_rows         the same contract for T <= 4 rows: one warp per weight row, 16-byte loads
+//   gemm_mma          the same interface on the tensor cores for bf16 weights (activations rounded to bf16 as they are staged)
+//   gemv_rows         the same interface for T <= 4 rows: one warp per weight row, 16-byte loads
 //   causal_conv_silu  depthwise causal convolution over the chunk continuing from the carried (taps - 1) inputs, + SiLU
 //   ssd_scan          the state-space recurrence S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x, gated by silu(z)
 //   latent_swa_attn   softmax attention over a sliding window of cached latents with absorbed key up-projection
@@ -799,18 +799,17 @@ __global__ void moe_route(const float* __restrict__ logits, const float* __restr
   }
 }
 
-// Groups the `pairs` (token, slot) pairs of a chunk by expert: perm lists the pairs expert by expert (stable), tiles cuts every
-// expert's run into row tiles of at most `bm` rows {expert, first index into perm, rows}.  One CTA.
-__global__ void __launch_bounds__(256) moe_plan(const int* __restrict__ idx, int pairs, int E, int bm, int* __restrict__ perm,
-                                                int4* __restrict__ tiles, int* __restrict__ n_tiles) {
+// Groups the `pairs` (token, slot) pairs of a chunk by expert: perm lists the pairs expert by expert (in no particular order
+// inside an expert: every row is computed on its own), tiles cuts every expert's run into row tiles of at most `bm` rows
+// {expert, first index into perm, rows}.  One CTA: histogram, serial scan over the experts, placement.
+__global__ void __launch_bounds__(1024) moe_plan(const int* __restrict__ idx, int pairs, int E, int bm, int* __restrict__ perm,
+                                                 int4* __restrict__ tiles, int* __restrict__ n_tiles) {
   extern __shared__ int smi[];
   int* cnt = smi;            // [E]
   int* off = smi + E;        // [E]
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int c = 0;
-    for (int i = 0; i < pairs; i++) c += idx[i] == e ? 1 : 0;
-    cnt[e] = c;
-  }
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&cnt[idx[i]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
     int o = 0, nt = 0;
@@ -822,10 +821,7 @@ __global__ void __launch_bounds__(256) moe_plan(const int* __restrict__ idx, int
     *n_tiles = nt;
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int o = off[e];
-    for (int i = 0; i < pairs; i++) if (idx[i] == e) perm[o++] = i;
-  }
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) perm[atomicAdd(&off[idx[i]], 1)] = i;
 }
 
 __global__ void moe_combine(float* __restrict__ x, int ldx, const float* __restrict__ y, const float* __restrict__ wgt, int top,

@@ -535,7 +535,8 @@ static void launch_scan(const dsk_layer_spec& sp, const float* proj, int ld_proj
                         float* state, float* out, int T, cudaStream_t st) {
   const int H = sp.ssm_heads, P = sp.ssm_vdim, N = sp.ssm_state, G = sp.ssm_groups;
   const int inner = H * P;
-  const int PB = std::min(P, 64);
+  int PB = std::min(P, 64);   // value channels per CTA: fewer when the heads alone would leave most SMs idle
+  while (PB > 8 && H * ((P + PB - 1) / PB) < 256) PB /= 2;
   const dim3 grid((unsigned)H, (unsigned)((P + PB - 1) / PB));
   const int threads = ((PB * 8 + 31) / 32) * 32;
   const int TB = T >= 64 ? 64 : 16;   // tokens staged per round
@@ -676,7 +677,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         linear(S, bf, HEPI_STORE, Dn, pairs, st);
       } else {
         const int bm = bf ? 128 : 64;   // rows per tile of the product kernel that follows (gemm_mma / gemm_tiled)
-        moe_plan<<<1, 256, (size_t)2 * E * 4, st>>>(S->d_idx, pairs, E, bm, S->d_perm, S->d_tiles, S->d_ntiles);
+        moe_plan<<<1, 1024, (size_t)2 * E * 4, st>>>(S->d_idx, pairs, E, bm, S->d_perm, S->d_tiles, S->d_ntiles);
         S->launches++;
         G.tiles = S->d_tiles; G.n_tiles = S->d_ntiles; G.a_map = S->d_perm; G.a_div = top; G.c_map = S->d_perm;
         Dn.tiles = S->d_tiles; Dn.n_tiles = S->d_ntiles; Dn.a_map = S->d_perm; Dn.a_div = 1; Dn.c_map = S->d_perm;
