@@ -266,6 +266,11 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_row)));
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(256) gemm_mma(const GemmP P) {
   typedef __nv_bfloat16 bf;
@@ -367,20 +372,18 @@ __global__ void __launch_bounds__(256) gemm_mma(const GemmP P) {
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
       uint32_t af[4][4], bfr[4][2];
-      const int c = kk + (lane & 3) * 2;
+      // ldmatrix: lanes 0-7 / 8-15 / 16-23 / 24-31 address the rows of the four 8 x 8 blocks of a fragment
 #pragma unroll
       for (int mi = 0; mi < 4; mi++) {
-        const int r = wm * 64 + mi * 16 + (lane >> 2);
-        af[mi][0] = *reinterpret_cast<const uint32_t*>(&As[r][c]);
-        af[mi][1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][c]);
-        af[mi][2] = *reinterpret_cast<const uint32_t*>(&As[r][c + 8]);
-        af[mi][3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][c + 8]);
+        const int r = wm * 64 + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4(af[mi], &As[r][kk + (lane >> 4) * 8]);                     // {rows 0-7, k 0-7}, {rows 8-15, k 0-7}, {rows 0-7, k 8-15}, {rows 8-15, k 8-15}
       }
 #pragma unroll
-      for (int ni = 0; ni < 4; ni++) {
-        const int n = wn * 32 + ni * 8 + (lane >> 2);
-        bfr[ni][0] = *reinterpret_cast<const uint32_t*>(&Bs[n][c]);
-        bfr[ni][1] = *reinterpret_cast<const uint32_t*>(&Bs[n][c + 8]);
+      for (int np = 0; np < 2; np++) {
+        uint32_t t[4];
+        const int n = wn * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8;
+        ldmatrix_x4(t, &Bs[n][kk + ((lane >> 3) & 1) * 8]);                    // {n 0-7, k 0-7}, {n 0-7, k 8-15}, {n 8-15, k 0-7}, {n 8-15, k 8-15}
+        bfr[2 * np][0] = t[0]; bfr[2 * np][1] = t[1]; bfr[2 * np + 1][0] = t[2]; bfr[2 * np + 1][1] = t[3];
       }
 #pragma unroll
       for (int mi = 0; mi < 4; mi++)
@@ -536,33 +539,37 @@ __global__ void conv_history_update(const float* __restrict__ in, int ld_in, flo
 
 // ---------------------------------------------------------------------------------------------------------------------
 // State-space-duality recurrence over a chunk, one CTA per (head, slice of PB value channels), sequential over the tokens.
-// Thread (pl, s) owns value channel p = p0 + pl and the state entries n = s, s + 8, ... (R of them) of S[h][p][:] in registers;
+// Thread (pl, s) owns value channel p = p0 + pl and 4 RQ entries of S[h][p][:] (groups of four consecutive n) in registers;
 // the eight threads of a channel reduce y with shuffles.  Inputs of TB tokens at a time are staged in shared memory.
 //   dt = softplus(raw_dt + dt_bias_h);  S <- exp(-exp(A_log_h) dt) S + dt B x^T;  y = S^T C + D_h x;  out = y silu(z)
 // proj: the input projection's rows [z | . | . | . | raw dt]; xbc: the convolved [x | B | C] rows.  Head h reads B/C group h / (H / G).
 // ---------------------------------------------------------------------------------------------------------------------
-template <int R>
+template <int RQ>
 __global__ void __launch_bounds__(512) ssd_scan(const float* __restrict__ proj, int ld_proj, int z_off, int dt_off,
                                                 const float* __restrict__ xbc, int ld_xbc, int x_off, int b_off, int c_off,
                                                 const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                                                 const float* __restrict__ Dskip, float* __restrict__ state,
                                                 float* __restrict__ out, int ld_out, int T, int H, int P, int N, int G, int PB, int TB) {
-  extern __shared__ float sm[];
-  float* s_dt = sm;                 // [TB]
-  float* s_dA = s_dt + TB;          // [TB]
-  float* s_B = s_dA + TB;           // [TB][N]
-  float* s_C = s_B + TB * N;        // [TB][N]
-  float* s_x = s_C + TB * N;        // [TB][PB]
+  extern __shared__ __align__(16) float sm[];
+  const int NP = (N + 3) & ~3;      // staged B / C rows are padded to whole float4s
+  float* s_B = sm;                  // [TB][NP]
+  float* s_C = s_B + TB * NP;       // [TB][NP]
+  float* s_x = s_C + TB * NP;       // [TB][PB]
   float* s_z = s_x + TB * PB;       // [TB][PB]
+  float* s_dt = s_z + TB * PB;      // [TB]
+  float* s_dA = s_dt + TB;          // [TB]
   const int h = blockIdx.x, p0 = blockIdx.y * PB, g = h / (H / G);
   const int tid = threadIdx.x, pl = tid >> 3, s = tid & 7, p = p0 + pl;
   const bool pok = pl < PB && p < P;
-  float S[R];
+  // thread (pl, s) owns the state entries n = 4 (s + 8 j) + q, j < RQ, q < 4: one 16-byte shared-memory read per j and operand
+  float S[RQ][4];
 #pragma unroll
-  for (int r = 0; r < R; r++) {
-    const int n = s + 8 * r;
-    S[r] = (pok && n < N) ? state[((size_t)h * P + p) * N + n] : 0.f;
-  }
+  for (int j = 0; j < RQ; j++)
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      const int n = 4 * (s + 8 * j) + q;
+      S[j][q] = (pok && n < N) ? state[((size_t)h * P + p) * N + n] : 0.f;
+    }
   const float a = -expf(A_log[h]), dsk = Dskip[h], dtb = dt_bias[h];
   for (int t0 = 0; t0 < T; t0 += TB) {
     const int nt = min(TB, T - t0);
@@ -572,10 +579,10 @@ __global__ void __launch_bounds__(512) ssd_scan(const float* __restrict__ proj, 
       s_dt[i] = dt;
       s_dA[i] = expf(a * dt);
     }
-    for (int i = tid; i < nt * N; i += blockDim.x) {
-      const int tt = i / N, n = i - tt * N;
-      s_B[i] = xbc[(size_t)(t0 + tt) * ld_xbc + b_off + g * N + n];
-      s_C[i] = xbc[(size_t)(t0 + tt) * ld_xbc + c_off + g * N + n];
+    for (int i = tid; i < nt * NP; i += blockDim.x) {
+      const int tt = i / NP, n = i - tt * NP;
+      s_B[i] = n < N ? xbc[(size_t)(t0 + tt) * ld_xbc + b_off + g * N + n] : 0.f;
+      s_C[i] = n < N ? xbc[(size_t)(t0 + tt) * ld_xbc + c_off + g * N + n] : 0.f;
     }
     for (int i = tid; i < nt * PB; i += blockDim.x) {
       const int tt = i / PB, q = i - tt * PB, pp = p0 + q;
@@ -587,15 +594,20 @@ __global__ void __launch_bounds__(512) ssd_scan(const float* __restrict__ proj, 
       const float dt = s_dt[tt], dA = s_dA[tt];
       const float xv = pl < PB ? s_x[tt * PB + pl] : 0.f;
       const float dx = dt * xv;
-      float y = 0.f;
+      float y0 = 0.f, y1 = 0.f;
 #pragma unroll
-      for (int r = 0; r < R; r++) {
-        const int n = s + 8 * r;
-        if (n < N) {
-          S[r] = fmaf(dA, S[r], dx * s_B[tt * N + n]);
-          y = fmaf(S[r], s_C[tt * N + n], y);
+      for (int j = 0; j < RQ; j++) {
+        const int n4 = 4 * (s + 8 * j);
+        if (n4 < NP) {   // entries past N are zero in the state and in the staged rows
+          const float4 b = *reinterpret_cast<const float4*>(s_B + tt * NP + n4);
+          const float4 c = *reinterpret_cast<const float4*>(s_C + tt * NP + n4);
+          S[j][0] = fmaf(dA, S[j][0], dx * b.x); S[j][1] = fmaf(dA, S[j][1], dx * b.y);
+          S[j][2] = fmaf(dA, S[j][2], dx * b.z); S[j][3] = fmaf(dA, S[j][3], dx * b.w);
+          y0 = fmaf(S[j][0], c.x, y0); y1 = fmaf(S[j][1], c.y, y1);
+          y0 = fmaf(S[j][2], c.z, y0); y1 = fmaf(S[j][3], c.w, y1);
         }
       }
+      float y = y0 + y1;
       y += __shfl_xor_sync(0xffffffffu, y, 1);
       y += __shfl_xor_sync(0xffffffffu, y, 2);
       y += __shfl_xor_sync(0xffffffffu, y, 4);
@@ -606,10 +618,12 @@ __global__ void __launch_bounds__(512) ssd_scan(const float* __restrict__ proj, 
     }
   }
 #pragma unroll
-  for (int r = 0; r < R; r++) {
-    const int n = s + 8 * r;
-    if (pok && n < N) state[((size_t)h * P + p) * N + n] = S[r];
-  }
+  for (int j = 0; j < RQ; j++)
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      const int n = 4 * (s + 8 * j) + q;
+      if (pok && n < N) state[((size_t)h * P + p) * N + n] = S[j][q];
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------

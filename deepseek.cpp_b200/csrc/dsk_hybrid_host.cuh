@@ -128,10 +128,8 @@ static void set_kernel_attrs() {
   cudaFuncSetAttribute(latent_swa_attn<float, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   cudaFuncSetAttribute(latent_swa_attn<float, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   cudaFuncSetAttribute(ssd_scan<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(ssd_scan<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-  cudaFuncSetAttribute(ssd_scan<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(ssd_scan<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-  cudaFuncSetAttribute(ssd_scan<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(ssd_scan<12>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-  cudaFuncSetAttribute(ssd_scan<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(ssd_scan<24>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-  cudaFuncSetAttribute(ssd_scan<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(ssd_scan<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(ssd_scan<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(ssd_scan<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(ssd_scan<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   done = true;
 }
 
@@ -540,13 +538,13 @@ static void launch_scan(const dsk_layer_spec& sp, const float* proj, int ld_proj
   const dim3 grid((unsigned)H, (unsigned)((P + PB - 1) / PB));
   const int threads = ((PB * 8 + 31) / 32) * 32;
   const int TB = T >= 64 ? 64 : 16;   // tokens staged per round
-  const size_t smem = (size_t)TB * (2 + 2 * N + 2 * PB) * 4;
-  const int need = (N + 7) / 8;
-#define DSK_SCAN(R) ssd_scan<R><<<grid, threads, smem, st>>>(proj, ld_proj, 0, inner + (int)ssd_channels(sp), xbc, ld_xbc, 0, inner, inner + G * N, \
-                                                             L.dt_bias, L.A_log, L.D, state, out, inner, T, H, P, N, G, PB, TB)
-  if (need <= 1) DSK_SCAN(1); else if (need <= 2) DSK_SCAN(2); else if (need <= 4) DSK_SCAN(4); else if (need <= 6) DSK_SCAN(6);
-  else if (need <= 8) DSK_SCAN(8); else if (need <= 12) DSK_SCAN(12); else if (need <= 16) DSK_SCAN(16); else if (need <= 24) DSK_SCAN(24);
-  else DSK_SCAN(32);
+  const int NP = (N + 3) & ~3;
+  const size_t smem = (size_t)TB * (2 + 2 * NP + 2 * PB) * 4;
+  const int need = (N + 31) / 32;     // float4 groups of state per thread
+#define DSK_SCAN(RQ) ssd_scan<RQ><<<grid, threads, smem, st>>>(proj, ld_proj, 0, inner + (int)ssd_channels(sp), xbc, ld_xbc, 0, inner, inner + G * N, \
+                                                               L.dt_bias, L.A_log, L.D, state, out, inner, T, H, P, N, G, PB, TB)
+  if (need <= 1) DSK_SCAN(1); else if (need <= 2) DSK_SCAN(2); else if (need <= 3) DSK_SCAN(3); else if (need <= 4) DSK_SCAN(4);
+  else if (need <= 6) DSK_SCAN(6); else DSK_SCAN(8);
 #undef DSK_SCAN
 }
 
