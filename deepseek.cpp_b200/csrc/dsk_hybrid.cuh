@@ -555,7 +555,7 @@ __global__ void __launch_bounds__(512) ssd_scan(const float* __restrict__ proj, 
   float* s_B = sm;                  // [TB][NP]
   float* s_C = s_B + TB * NP;       // [TB][NP]
   float* s_x = s_C + TB * NP;       // [TB][PB]
-  float* s_z = s_x + TB * PB;       // [TB][PB]
+  float* s_z = s_x + TB * PB;       // [TB][PB]  silu(z)
   float* s_dt = s_z + TB * PB;      // [TB]
   float* s_dA = s_dt + TB;          // [TB]
   const int h = blockIdx.x, p0 = blockIdx.y * PB, g = h / (H / G);
@@ -579,15 +579,38 @@ __global__ void __launch_bounds__(512) ssd_scan(const float* __restrict__ proj, 
       s_dt[i] = dt;
       s_dA[i] = expf(a * dt);
     }
-    for (int i = tid; i < nt * NP; i += blockDim.x) {
-      const int tt = i / NP, n = i - tt * NP;
-      s_B[i] = n < N ? xbc[(size_t)(t0 + tt) * ld_xbc + b_off + g * N + n] : 0.f;
-      s_C[i] = n < N ? xbc[(size_t)(t0 + tt) * ld_xbc + c_off + g * N + n] : 0.f;
+    // eight elements per thread and pass: all sixteen loads are in flight before the first is stored (the round is latency-bound)
+    for (int base = 0; base < nt * NP; base += 8 * (int)blockDim.x) {
+      float vb[8], vc[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int i = base + u * (int)blockDim.x + tid;
+        const int tt = i / NP, n = i - tt * NP;
+        const bool ok = i < nt * NP && n < N;
+        vb[u] = ok ? xbc[(size_t)(t0 + tt) * ld_xbc + b_off + g * N + n] : 0.f;
+        vc[u] = ok ? xbc[(size_t)(t0 + tt) * ld_xbc + c_off + g * N + n] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int i = base + u * (int)blockDim.x + tid;
+        if (i < nt * NP) { s_B[i] = vb[u]; s_C[i] = vc[u]; }
+      }
     }
-    for (int i = tid; i < nt * PB; i += blockDim.x) {
-      const int tt = i / PB, q = i - tt * PB, pp = p0 + q;
-      s_x[i] = pp < P ? xbc[(size_t)(t0 + tt) * ld_xbc + x_off + h * P + pp] : 0.f;
-      s_z[i] = pp < P ? proj[(size_t)(t0 + tt) * ld_proj + z_off + h * P + pp] : 0.f;
+    for (int base = 0; base < nt * PB; base += 8 * (int)blockDim.x) {
+      float vx[8], vz[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int i = base + u * (int)blockDim.x + tid;
+        const int tt = i / PB, q = i - tt * PB, pp = p0 + q;
+        const bool ok = i < nt * PB && pp < P;
+        vx[u] = ok ? xbc[(size_t)(t0 + tt) * ld_xbc + x_off + h * P + pp] : 0.f;
+        vz[u] = ok ? proj[(size_t)(t0 + tt) * ld_proj + z_off + h * P + pp] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int i = base + u * (int)blockDim.x + tid;
+        if (i < nt * PB) { s_x[i] = vx[u]; s_z[i] = silu_f(vz[u]); }   // the gate, off the sequential path
+      }
     }
     __syncthreads();
     for (int tt = 0; tt < nt; tt++) {
@@ -613,7 +636,7 @@ __global__ void __launch_bounds__(512) ssd_scan(const float* __restrict__ proj, 
       y += __shfl_xor_sync(0xffffffffu, y, 4);
       if (s == 0 && pok) {
         y = fmaf(dsk, xv, y);
-        out[(size_t)(t0 + tt) * ld_out + h * P + p] = y * silu_f(s_z[tt * PB + pl]);
+        out[(size_t)(t0 + tt) * ld_out + h * P + p] = y * s_z[tt * PB + pl];
       }
     }
   }

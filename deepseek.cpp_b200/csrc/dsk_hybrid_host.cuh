@@ -76,6 +76,11 @@ struct State {
   int *h_tok = nullptr, *h_want = nullptr;   // pinned staging of a chunk's token ids / wanted rows
   std::vector<void*> allocs;
   cudaGraphExec_t step_graph = nullptr;      // captured greedy decode step (arg-max -> token -> one-token chunk)
+  // DSK_HY_TIMELINE=1: CUDA events between the groups of launches of every step, summed per label and printed to stderr
+  bool timeline = false;
+  std::vector<cudaEvent_t> tl_events;
+  std::vector<const char*> tl_labels;
+  size_t tl_used = 0;
   long long launches = 0;
 };
 
@@ -383,6 +388,7 @@ static dsk_state* state_create(dsk_model* m) {
   s->m = m;
   s->hy = S;
   S->chunk = c.chunk;
+  S->timeline = getenv("DSK_HY_TIMELINE") != nullptr;
   const size_t Tc = c.chunk;
   // the pieces the shared sampling / arg-max code reads
   cudaMalloc((void**)&s->ctrl, sizeof(Ctrl)); cudaMemset(s->ctrl, 0, sizeof(Ctrl));
@@ -464,6 +470,7 @@ static void state_free(dsk_state* s) {
   State* S = s->hy;
   if (!S) return;
   if (S->step_graph) cudaGraphExecDestroy(S->step_graph);
+  for (cudaEvent_t e : S->tl_events) cudaEventDestroy(e);
   for (void* p : S->allocs) cudaFree(p);
   cudaFreeHost(S->h_tok); cudaFreeHost(S->h_want);
   delete S;
@@ -473,6 +480,29 @@ static void state_free(dsk_state* s) {
 // ---------------------------------------------------------------------------------------------------------------------
 // the chunk step
 // ---------------------------------------------------------------------------------------------------------------------
+// marks the end of a group of launches (timeline mode only; never inside a captured step)
+static void mark(State* S, const char* label, cudaStream_t st) {
+  if (!S->timeline) return;
+  if (S->tl_used == S->tl_events.size()) { cudaEvent_t e; cudaEventCreate(&e); S->tl_events.push_back(e); S->tl_labels.push_back(label); }
+  S->tl_labels[S->tl_used] = label;
+  cudaEventRecord(S->tl_events[S->tl_used++], st);
+}
+static void timeline_report(State* S, int T) {
+  if (!S->timeline || S->tl_used < 2) { S->tl_used = 0; return; }
+  cudaEventSynchronize(S->tl_events[S->tl_used - 1]);
+  std::map<std::string, double> sum;
+  double tot = 0;
+  for (size_t i = 1; i < S->tl_used; i++) {
+    float ms = 0;
+    cudaEventElapsedTime(&ms, S->tl_events[i - 1], S->tl_events[i]);
+    sum[S->tl_labels[i]] += ms; tot += ms;
+  }
+  fprintf(stderr, "[dsk timeline] step of %d tokens: %.3f ms |", T, tot);
+  for (auto& kv : sum) fprintf(stderr, " %s %.3f", kv.first.c_str(), kv.second);
+  fprintf(stderr, "\n");
+  S->tl_used = 0;
+}
+
 static GemmP gp(const float* A, int lda, const void* W, int ldw, float* C, int ldc, int M, int N, int K) {
   GemmP P{};
   P.A = A; P.lda = lda; P.W = W; P.ldw = ldw; P.C = C; P.ldc = ldc; P.M = M; P.N = N; P.K = K;
@@ -534,7 +564,8 @@ static void launch_scan(const dsk_layer_spec& sp, const float* proj, int ld_proj
   const int H = sp.ssm_heads, P = sp.ssm_vdim, N = sp.ssm_state, G = sp.ssm_groups;
   const int inner = H * P;
   int PB = std::min(P, 64);   // value channels per CTA: fewer when the heads alone would leave most SMs idle
-  while (PB > 8 && H * ((P + PB - 1) / PB) < 256) PB /= 2;
+  while (PB > 32 && H * ((P + PB - 1) / PB) < 148) PB /= 2;   // (measured: 32 channels per CTA is the best split at 64 heads x 64)
+  if (const char* e = getenv("DSK_SCAN_PB")) PB = std::max(1, std::min(std::min(P, 64), atoi(e)));   // A/B switch
   const dim3 grid((unsigned)H, (unsigned)((P + PB - 1) / PB));
   const int threads = ((PB * 8 + 31) / 32) * 32;
   const int TB = T >= 64 ? 64 : 16;   // tokens staged per round
@@ -590,6 +621,10 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
   if (bf) embed_rows<__nv_bfloat16><<<T, 256, 0, st>>>(S->d_tok, (const __nv_bfloat16*)M->embed.p, W, S->x);
   else embed_rows<float><<<T, 256, 0, st>>>(S->d_tok, (const float*)M->embed.p, W, S->x);
   S->launches++;
+  if (pos0 < 0) S->tl_used = 0;   // a captured step records no events
+  const bool tl = S->timeline && pos0 >= 0;
+  auto MK = [&](const char* label) { if (tl) mark(S, label, st); };
+  MK("embed");
   for (int li = 0; li < c.n_layers; li++) {
     const HLayer& L = M->L[li];
     const dsk_layer_spec& sp = L.sp;
@@ -598,25 +633,33 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
     S->launches++;
     if (is_ssd(sp)) {
       const int inner = (int)ssd_inner(sp), ch = (int)ssd_channels(sp), pw = (int)ssd_proj(sp);
+      MK("norm");
       linear(S, bf, HEPI_STORE, gp(S->h, W, L.in.p, W, S->b0, pw, T, pw, W), 1, st);
+      MK("ssd.in");
       causal_conv_silu<<<dim3((unsigned)((ch + 127) / 128), (unsigned)T), 128, 0, st>>>(S->b0 + inner, pw, L.conv_w, L.conv_b, ls.hist, S->b1, ch, T, ch, sp.ssm_conv);
       if (sp.ssm_conv > 1) conv_history_update<<<(ch + 127) / 128, 128, 0, st>>>(S->b0 + inner, pw, ls.hist, T, ch, sp.ssm_conv);
+      MK("ssd.conv");
       launch_scan(sp, S->b0, pw, S->b1, ch, L, ls.ssm, S->b2, T, st);
+      MK("ssd.scan");
       group_rmsnorm<float><<<T, 256, 0, st>>>(S->b2, inner, L.mnorm, S->b3, inner, inner, sp.ssm_norm_groups, c.norm_eps, 0, 0.f, nullptr, 0);
       S->launches += 4;
+      MK("ssd.norm");
       GemmP P = gp(S->b3, inner, L.o.p, inner, S->x, W, T, W, inner);
       P.alpha = mult;
       linear(S, bf, HEPI_ADD, P, 1, st);
+      MK("ssd.o");
     } else {
       const int H = sp.att_heads, D = sp.att_dim, V = sp.att_vdim, R = sp.att_kv_rank;
       const HLayer& O = M->L[L.owner];
       float* cache = (float*)S->L[L.owner].cache;
+      MK("norm");
       linear(S, bf, HEPI_STORE, gp(S->h, W, L.q.p, W, S->b0, H * D, T, H * D, W), 1, st);
       if (L.owner == li) {
         linear(S, bf, HEPI_STORE, gp(S->h, W, L.dkv.p, W, S->b1, R, T, R, W), 1, st);
         group_rmsnorm<float><<<T, 256, 0, st>>>(S->b1, R, L.dkv_norm, cache, R, R, 1, c.norm_eps, 0, 0.f, S->d_ctl, O.ring);
         S->launches++;
       }
+      MK("att.q+latent");
       const float* ov = S->b0;   // [T][H*V] heads' outputs
       if (pos0 >= 0 && T >= kPrefillMin && S->prefill_keys > 0) {
         // a portion: blocks of kPrefillQ queries, each as  k, v = up-projections of the visible latents;  P = softmax_band(q k^T);  o = P v
@@ -631,15 +674,20 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
           GemmP Vp = gp(cache, R, L.uv.p, R, S->vf, H * V, Lk, H * V, R);
           Vp.a_map = S->d_rows;
           linear(S, bf, HEPI_STORE, Vp, 1, st);
+          MK("att.kv_up");
           if (bf) pack_keys_values<__nv_bfloat16><<<Lk, 256, 0, st>>>(S->kf, S->vf, (__nv_bfloat16*)S->kb, (__nv_bfloat16*)S->vt, Lk, H, D, V);
           else pack_keys_values<float><<<Lk, 256, 0, st>>>(S->kf, S->vf, (float*)S->kb, (float*)S->vt, Lk, H, D, V);
           GemmP Sc = gp(S->b0 + (size_t)t0 * H * D, H * D, S->kb, D, S->sc, Lk, Tq, Lk, D);
           Sc.sA = D; Sc.sW = (long long)Lk * D; Sc.sC = (long long)Tq * Lk; Sc.alpha = sp.att_scale;
+          MK("att.pack");
           linear(S, bf, HEPI_STORE, Sc, H, st);
+          MK("att.scores");
           softmax_band<<<dim3((unsigned)Tq, (unsigned)H), 128, 0, st>>>(S->sc, Tq, Lk, first, qpos0, sp.att_window);
           GemmP Ov = gp(S->sc, Lk, S->vt, Lk, S->b3 + (size_t)t0 * H * V, H * V, Tq, V, Lk);
           Ov.sA = (long long)Tq * Lk; Ov.sW = (long long)V * Lk; Ov.sC = V;
+          MK("att.softmax");
           linear(S, bf, HEPI_STORE, Ov, H, st);
+          MK("att.pv");
           S->launches += 3;
         }
       } else {
@@ -656,15 +704,18 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
           linear(S, bf, HEPI_STORE, P, H, st);
         }
       }
+      MK("att.absorbed");
       GemmP P = gp(ov, H * V, L.o.p, H * V, S->x, W, T, W, H * V);
       P.alpha = mult;
       linear(S, bf, HEPI_ADD, P, 1, st);
+      MK("att.o");
     }
     if (sp.ff_kind == DSK_FF_MOE) {
       const int E = sp.ff_experts, top = sp.ff_top, ff = sp.ff_hidden, pairs = T * top;
       linear(S, false, HEPI_STORE, gp(S->h, W, L.router, W, S->b0, E, T, E, W), 1, st);   // router: fp32 weights in every mode
       moe_route<<<T, 128, (size_t)(2 * E + top) * 4, st>>>(S->b0, L.correction, E, top, sp.ff_router_scale, S->d_idx, S->wgt);
       S->launches++;
+      MK("moe.router");
       GemmP G = gp(S->h, W, L.gate_s.p, W, S->b2, ff, pairs, ff, W);
       G.W2 = L.up_s.p; G.sW = (long long)ff * W; G.lim = sp.ff_limit;
       GemmP Dn = gp(S->b2, ff, L.down_s.p, ff, S->b3, W, pairs, W, ff);
@@ -672,7 +723,9 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       if (T <= 4) {
         G.z_expert = S->d_idx; G.z_adiv = top; Dn.z_expert = S->d_idx; Dn.z_adiv = 1;
         linear(S, bf, HEPI_GLU, G, pairs, st);
+        MK("moe.glu");
         linear(S, bf, HEPI_STORE, Dn, pairs, st);
+        MK("moe.down");
       } else {
         const int bm = bf ? 128 : 64;   // rows per tile of the product kernel that follows (gemm_mma / gemm_tiled)
         moe_plan<<<1, 1024, (size_t)2 * E * 4, st>>>(S->d_idx, pairs, E, bm, S->d_perm, S->d_tiles, S->d_ntiles);
@@ -680,11 +733,15 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         G.tiles = S->d_tiles; G.n_tiles = S->d_ntiles; G.a_map = S->d_perm; G.a_div = top; G.c_map = S->d_perm;
         Dn.tiles = S->d_tiles; Dn.n_tiles = S->d_ntiles; Dn.a_map = S->d_perm; Dn.a_div = 1; Dn.c_map = S->d_perm;
         const int cap = std::min(S->max_tiles, pairs / bm + E + 1);
+        MK("moe.plan");
         linear(S, bf, HEPI_GLU, G, 1, st, cap);
+        MK("moe.glu");
         linear(S, bf, HEPI_STORE, Dn, 1, st, cap);
+        MK("moe.down");
       }
       moe_combine<<<T, 256, 0, st>>>(S->x, W, S->b3, S->wgt, top, W, mult);
       S->launches++;
+      MK("moe.combine");
     }
     if (c.side_dim > 0) {
       const int sd = c.side_dim;
@@ -694,6 +751,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       linear(S, bf, HEPI_STORE, gp(S->b1, sd, L.sproj.p, sd, S->h, W, T, W, sd), 1, st);
       group_rmsnorm<float><<<T, 256, 0, st>>>(S->h, W, L.snorm, S->x, W, W, 1, c.norm_eps, 1, mult, nullptr, 0);
       S->launches++;
+      MK("side");
     }
     if (trace) CKL(cudaMemcpyAsync(trace + (size_t)li * T * W, S->x, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st));
   }
@@ -701,6 +759,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
     group_rmsnorm<float><<<T, 256, 0, st>>>(S->x, W, M->final_norm, S->h, W, W, c.norm_groups, c.norm_eps, 0, 0.f, nullptr, 0);
     S->launches++;
     enqueue_head(m, s, 0, std::min(n_want, S->head_rows), st);
+    MK("head");
   }
   CKL(cudaGetLastError());
   return 0;
@@ -743,6 +802,7 @@ static int forward_chunk(dsk_model* m, dsk_state* s, const int32_t* tokens, int 
       CK(cudaMemcpyAsync(s->logits, S->logits + (size_t)((nw - 1) % S->head_rows) * c.vocab_size, (size_t)c.vocab_size * 4, cudaMemcpyDeviceToDevice, s->stream));
       argmax_row<<<1, 1024, 0, s->stream>>>(s->logits, c.vocab_size, s->ctrl, nullptr, nullptr, 0);
     }
+    timeline_report(S, T);
     if (host_layers) {
       CK(cudaStreamSynchronize(s->stream));
       for (int l = 0; l < c.n_layers; l++)
