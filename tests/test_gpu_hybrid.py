@@ -291,6 +291,11 @@ def test_other_sizes(mk, ho, case):
     assert rel(got, exp) < F32_TOL
     rows = [m.forward_chunk(toks[:20], 0, range(20))] + [m.forward_chunk(toks[i:i + 1], i, [0]) for i in range(20, 45)]
     assert rel(np.concatenate(rows), exp) < F32_TOL
+    if case != "wide":      # the bfloat16 kernels on the same sizes: unaligned rows and K tails take their scalar paths
+        mb, _ = mk(cfg, seed=31, chunk=64, quant="bf16")
+        assert close_bf16(mb.forward_chunk(toks, 0, range(45)), exp)
+        rows = [mb.forward_chunk(toks[:20], 0, range(20))] + [mb.forward_chunk(toks[i:i + 1], i, [0]) for i in range(20, 45)]
+        assert close_bf16(np.concatenate(rows), exp)
 
 
 def test_large_steps_and_many_wanted_rows(mk, ho):
@@ -379,3 +384,16 @@ def test_cli_completion(full, repo):
     m.forward_chunk(prompt, 0, [len(prompt) - 1])
     dev, _ = m.decode_greedy(len(prompt), steps)
     assert ids[len(prompt):] == dev.tolist()
+
+
+def test_forward_chunk_on_deepseek_models(ckpt):
+    """dsk_forward_chunk is the framework's portion call for every family: a DeepSeek model runs its hydrate loop inside it."""
+    import dsk
+    m = dsk.Model.from_dir(ckpt("tiny_v2lite", "fp32"))
+    toks = [0, 17, 300, 5, 9]
+    rows = [m.forward(t, i)[0].copy() for i, t in enumerate(toks)]
+    got = m.forward_chunk(toks, 0, [1, 4])
+    assert np.array_equal(got[0], rows[1]) and np.array_equal(got[1], rows[4])
+    m.reset()
+    assert np.array_equal(m.forward_chunk(toks[:2], 0, [1])[0], rows[1])
+    m.close()
