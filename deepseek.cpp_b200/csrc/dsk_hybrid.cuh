@@ -271,14 +271,25 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_r
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_row)));
 }
 
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc, int src_bytes) {   // bytes past src_bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int kMmaStages = 4;                                   // weight tiles in flight (cp.async ring)
+constexpr int kMmaPitch = 40;                                   // bf16 per staged row: 32 + 8 (ldmatrix rows fall on distinct banks)
+constexpr size_t kMmaSmem = (size_t)(1 + kMmaStages) * 128 * kMmaPitch * 2;
+
 template <int EPI>
 __global__ void __launch_bounds__(256) gemm_mma(const GemmP P) {
   typedef __nv_bfloat16 bf;
-  constexpr int BM = 128, BT = 128, BK = 32, PITCH = BK + 8;
+  constexpr int BM = 128, BT = 128, BK = 32, PITCH = kMmaPitch, ST = kMmaStages;
   constexpr bool DUAL = EPI == HEPI_GLU;
   constexpr int BN = DUAL ? 64 : 128;
-  __shared__ __align__(16) bf As[BM][PITCH];
-  __shared__ __align__(16) bf Bs[BT][PITCH];
+  extern __shared__ __align__(16) unsigned char smraw[];
+  bf (*As)[PITCH] = reinterpret_cast<bf (*)[PITCH]>(smraw);                                  // [BM][PITCH]
+  bf (*Bs)[BT][PITCH] = reinterpret_cast<bf (*)[BT][PITCH]>(smraw + (size_t)BM * PITCH * 2);   // [ST][BT][PITCH]
   __shared__ int rowsA[BM], rowsC[BM];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   long long aoff = (long long)blockIdx.z * P.sA, woff = (long long)blockIdx.z * P.sW, coff = (long long)blockIdx.z * P.sC;
@@ -323,9 +334,10 @@ __global__ void __launch_bounds__(256) gemm_mma(const GemmP P) {
     for (int j = 0; j < 4; j++)
 #pragma unroll
       for (int q = 0; q < 4; q++) acc[i][j][q] = 0.f;
-  // the next K step's global loads are issued before the current step's tensor-core work and parked in registers
-  uint32_t ra[8], rb[8];
-  auto fetch = [&](int k0) {
+  // The weight stream (from HBM) runs ST - 1 steps ahead through a cp.async ring; the activations (small, L2-resident, fp32 -> bf16
+  // on the way) run one step ahead through registers.
+  uint32_t ra[8];
+  auto fetch_a = [&](int k0) {
     const int kb = k0 + lk;
     if (ar >= 0 && vecA && kb + 16 <= P.K) {
       const float4* src = reinterpret_cast<const float4*>(A + (size_t)ar * P.lda + kb);
@@ -345,30 +357,41 @@ __global__ void __launch_bounds__(256) gemm_mma(const GemmP P) {
         ra[q] = *reinterpret_cast<const uint32_t*>(&pr);
       }
     }
-    if (wrow_ok && vecB && kb + 16 <= P.K) {
-      const uint4* src = reinterpret_cast<const uint4*>(wsrc + (size_t)wrow * P.ldw + kb);
-      const uint4 u0 = src[0], u1 = src[1];
-      rb[0] = u0.x; rb[1] = u0.y; rb[2] = u0.z; rb[3] = u0.w; rb[4] = u1.x; rb[5] = u1.y; rb[6] = u1.z; rb[7] = u1.w;
+  };
+  auto issue_w = [&](int k0, int stage) {   // this thread's 16 weights of K step k0 -> Bs[stage]
+    bf* dst = &Bs[stage][lr][lk];
+    const int kb = k0 + lk;
+    if (vecB) {
+      const bool in = wrow_ok && kb < P.K;
+      const bf* src = in ? wsrc + (size_t)wrow * P.ldw + kb : wsrc;
+      const int left = in ? (P.K - kb) * 2 : 0;                       // valid bytes from kb on
+      cp_async_16(dst, src, max(0, min(16, left)));
+      cp_async_16(dst + 8, in && left > 16 ? src + 8 : wsrc, max(0, min(16, left - 16)));
     } else {
       const unsigned short* ws = reinterpret_cast<const unsigned short*>(wsrc);
+      unsigned short* d = reinterpret_cast<unsigned short*>(dst);
 #pragma unroll
-      for (int q = 0; q < 8; q++) {
-        const uint32_t v0 = (wrow_ok && kb + 2 * q < P.K) ? ws[(size_t)wrow * P.ldw + kb + 2 * q] : 0u;
-        const uint32_t v1 = (wrow_ok && kb + 2 * q + 1 < P.K) ? ws[(size_t)wrow * P.ldw + kb + 2 * q + 1] : 0u;
-        rb[q] = v0 | (v1 << 16);
-      }
+      for (int q = 0; q < 16; q++) d[q] = (wrow_ok && kb + q < P.K) ? ws[(size_t)wrow * P.ldw + kb + q] : (unsigned short)0;
     }
   };
-  fetch(0);
-  for (int k0 = 0; k0 < P.K; k0 += BK) {
+  const int nk = (P.K + BK - 1) / BK;
+#pragma unroll
+  for (int st = 0; st < ST - 1; st++) {
+    if (st < nk) issue_w(st * BK, st);
+    cp_async_commit();
+  }
+  fetch_a(0);
+  for (int kt = 0; kt < nk; kt++) {
     {
       uint4* da = reinterpret_cast<uint4*>(&As[lr][lk]);
       da[0] = make_uint4(ra[0], ra[1], ra[2], ra[3]); da[1] = make_uint4(ra[4], ra[5], ra[6], ra[7]);
-      uint4* db = reinterpret_cast<uint4*>(&Bs[lr][lk]);
-      db[0] = make_uint4(rb[0], rb[1], rb[2], rb[3]); db[1] = make_uint4(rb[4], rb[5], rb[6], rb[7]);
     }
+    cp_async_wait<ST - 2>();          // the weights of step kt have landed (one group per step, empty ones included)
     __syncthreads();
-    if (k0 + BK < P.K) fetch(k0 + BK);
+    if (kt + ST - 1 < nk) issue_w((kt + ST - 1) * BK, (kt + ST - 1) % ST);   // into the buffer step kt - 1 has finished reading
+    cp_async_commit();
+    if (kt + 1 < nk) fetch_a((kt + 1) * BK);
+    const int sb = kt % ST;
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
       uint32_t af[4][4], bfr[4][2];
@@ -382,7 +405,7 @@ __global__ void __launch_bounds__(256) gemm_mma(const GemmP P) {
       for (int np = 0; np < 2; np++) {
         uint32_t t[4];
         const int n = wn * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8;
-        ldmatrix_x4(t, &Bs[n][kk + ((lane >> 3) & 1) * 8]);                    // {n 0-7, k 0-7}, {n 0-7, k 8-15}, {n 8-15, k 0-7}, {n 8-15, k 8-15}
+        ldmatrix_x4(t, &Bs[sb][n][kk + ((lane >> 3) & 1) * 8]);                // {n 0-7, k 0-7}, {n 0-7, k 8-15}, {n 8-15, k 0-7}, {n 8-15, k 8-15}
         bfr[2 * np][0] = t[0]; bfr[2 * np][1] = t[1]; bfr[2 * np + 1][0] = t[2]; bfr[2 * np + 1][1] = t[3];
       }
 #pragma unroll

@@ -135,6 +135,10 @@ static void set_kernel_attrs() {
   cudaFuncSetAttribute(ssd_scan<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(ssd_scan<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   cudaFuncSetAttribute(ssd_scan<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(ssd_scan<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   cudaFuncSetAttribute(ssd_scan<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(ssd_scan<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(gemm_mma<HEPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
+  cudaFuncSetAttribute(gemm_mma<HEPI_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
+  cudaFuncSetAttribute(gemm_mma<HEPI_GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
+  cudaFuncSetAttribute(gemm_mma<HEPI_GELU_MUL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
   done = true;
 }
 
@@ -514,10 +518,10 @@ static void launch_gemm_mma(int epi, const GemmP& P, int Z, int tile_cap, cudaSt
   const int bn = epi == HEPI_GLU ? 64 : 128;
   const dim3 grid((unsigned)((P.N + bn - 1) / bn), (unsigned)(P.tiles ? tile_cap : (P.M + 127) / 128), (unsigned)Z);
   switch (epi) {
-    case HEPI_STORE: gemm_mma<HEPI_STORE><<<grid, 256, 0, st>>>(P); break;
-    case HEPI_ADD: gemm_mma<HEPI_ADD><<<grid, 256, 0, st>>>(P); break;
-    case HEPI_GLU: gemm_mma<HEPI_GLU><<<grid, 256, 0, st>>>(P); break;
-    default: gemm_mma<HEPI_GELU_MUL><<<grid, 256, 0, st>>>(P); break;
+    case HEPI_STORE: gemm_mma<HEPI_STORE><<<grid, 256, kMmaSmem, st>>>(P); break;
+    case HEPI_ADD: gemm_mma<HEPI_ADD><<<grid, 256, kMmaSmem, st>>>(P); break;
+    case HEPI_GLU: gemm_mma<HEPI_GLU><<<grid, 256, kMmaSmem, st>>>(P); break;
+    default: gemm_mma<HEPI_GELU_MUL><<<grid, 256, kMmaSmem, st>>>(P); break;
   }
 }
 
