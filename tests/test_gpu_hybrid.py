@@ -397,3 +397,68 @@ def test_forward_chunk_on_deepseek_models(ckpt):
     m.reset()
     assert np.array_equal(m.forward_chunk(toks[:2], 0, [1])[0], rows[1])
     m.close()
+
+
+def random_design(seed):
+    """A random model of the family: layer order, every size, windows, sharing of latent caches and constants drawn at random."""
+    r = np.random.RandomState(seed)
+    div = lambda n: int(r.choice([d for d in range(1, n + 1) if n % d == 0]))
+    parts = lambda n: int(r.choice([d for d in range(1, n + 1) if n % d == 0 and (n // d >= 4 or d == 1)]))   # norm groups of 4 values and more:
+    # a norm over one or two values is a sign function, which turns rounding noise into O(1) differences
+    width = int(r.choice([24, 36, 40, 56, 72, 96, 130]))
+    layers, owners = [], []
+    for i in range(int(r.randint(2, 8))):
+        ff = None
+        if r.rand() < 0.7:
+            E = int(r.randint(2, 21))
+            ff = moe(E=E, top=int(r.randint(1, min(E, 4) + 1)), ff=int(r.randint(4, 50)), lim=float(r.uniform(0.5, 4.0)), sc=float(r.uniform(0.5, 2.5)))
+        if r.rand() < 0.5:
+            heads = int(r.randint(1, 9))
+            vdim = int(r.randint(3, 41))
+            layers.append(ssd_layer(heads=heads, vdim=vdim, state=int(r.randint(4, 71)), groups=div(heads), conv=int(r.randint(1, 6)),
+                                    ng=parts(heads * vdim) if r.rand() < 0.5 else 1, mlp=ff, typ=str(r.choice(["mamba2", "mamba2_2"]))))
+        else:
+            src = None
+            rank = int(r.randint(8, 101))
+            if owners and r.rand() < 0.4:
+                src = int(r.choice(owners))
+                rank = layers[src]["mixer"]["kv_rank"]
+            else:
+                owners.append(i)
+            layers.append(att_layer(heads=int(r.randint(1, 8)), dim=int(r.randint(4, 41)), vdim=int(r.randint(4, 41)), rank=rank,
+                                    win=int(r.choice([1, 2, 3, 7, 16, 31, 32, 33, 50, 80])), scale=float(r.uniform(0.1, 0.6)), src=src, mlp=ff))
+    return model_cfg(layers, width=width, vocab=int(r.randint(5, 200)), groups=parts(width) if r.rand() < 0.7 else 1,
+                     side=int(r.randint(2, 13)) if r.rand() < 0.6 else 0, m=float(r.uniform(0.3, 1.0)), ls=float(r.uniform(0.5, 2.0)))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_designs(mk, ho, seed):
+    """Whole prompt, prompt + decoded tail, and uneven portions (both attention paths, the internal step boundary at 64) of a random
+    design against the oracle, in fp32; then the bfloat16 kernels on the same model."""
+    cfg = random_design(100 + seed)
+    m, W = mk(cfg, seed=seed, chunk=64)
+    n = 150
+    toks = tokens_for(cfg, n, seed)
+    exp = ho.run(cfg, W, toks)[0]
+    assert rel(m.forward_chunk(toks, 0, range(n)), exp) < F32_TOL
+    rows = [m.forward_chunk(toks[:110], 0, range(110))] + [m.forward_chunk(toks[i:i + 1], i, [0]) for i in range(110, n)]
+    assert rel(np.concatenate(rows), exp) < F32_TOL
+    r, p, rows = np.random.RandomState(seed), 0, []
+    while p < n:
+        c = min(int(r.choice([2, 3, 5, 17, 33, 40, 64, 70])), n - p)
+        rows.append(m.forward_chunk(toks[p:p + c], p, range(c)))
+        p += c
+    assert rel(np.concatenate(rows), exp) < F32_TOL
+    # bfloat16 matrices.  Steps of up to 4 tokens multiply them with the fp32 activations: the weights are exact in bfloat16, so
+    # this path must agree as tightly as the fp32 one.  Larger steps round the activations to bfloat16 on the way into the tensor
+    # cores: small random models magnify that (and a routed layer may flip a near-tied expert), so only the bulk is bounded —
+    # a wrong kernel is off by O(1) in every row.
+    mb, _ = mk(cfg, seed=seed, chunk=64, quant="bf16")
+    rows, p = [], 0
+    while p < 60:
+        c = min(int(r.choice([1, 2, 3, 4])), 60 - p)
+        rows.append(mb.forward_chunk(toks[p:p + c], p, range(c)))
+        p += c
+    assert rel(np.concatenate(rows), exp[:60]) < F32_TOL
+    e = np.abs(mb.forward_chunk(toks, 0, range(n)) - exp).max(-1) / np.abs(exp).max()
+    assert np.median(e) < 6e-2
