@@ -2194,6 +2194,11 @@ extern "C" dsk_model* dsk_model_create_hybrid(const dsk_hybrid_config* cfg, cons
   return hyb::model_create(cfg, layers, rank, n_ranks);
 }
 
+extern "C" int dsk_model_layer_runs(const dsk_model* m) {
+  if (!m) return fail(-4, "bad arguments");
+  return m->hy ? (int)m->hy->runs.size() : m->c.n_layers;
+}
+
 extern "C" int dsk_state_reset(dsk_state* s) {
   if (need_device()) return -1;
   if (!s) return fail(-1, "null state");

@@ -14,9 +14,15 @@
 //   causal_conv_silu  depthwise causal convolution over the chunk continuing from the carried (taps - 1) inputs, + SiLU
 //   ssd_scan          the state-space recurrence S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x, gated by silu(z)
 //   latent_swa_attn   softmax attention over a sliding window of cached latents with absorbed key up-projection
+//   layer_norm        (x - mean) / sqrt(var + eps) * w, stored or added into the residual
+//   qk_norm_rope      RMS norm over a whole query / key projection, partial interleaved rotary positions from a frequency table,
+//                     keys and values written into their ring caches
+//   gqa_attn          softmax attention of grouped query heads over ring caches of keys and values with a window or chunk mask
+//                     and optional mixing of the heads' scores before the softmax (decode-sized steps)
+//   pack_ring_kv, mix_heads, softmax_band   the same attention for portions, between three matrix products
 //   moe_route         sigmoid scores, selection by score + correction, weights = normalised scores x scale
 //   moe_plan          groups the (token, slot) pairs of a chunk by expert into row tiles for gemm_tiled
-//   moe_combine       residual += alpha * sum_k w_k y_k
+//   moe_combine       residual += alpha * sum_k w_k y_k (or stored, when a norm follows)
 //
 // Numerics: the residual stream, norms, router, softmax, recurrent state, decays, step sizes and gates are fp32 in every mode;
 // DSK_BF16 models keep their matrices in bfloat16 and accumulate in fp32: decode-sized products multiply them with the fp32
@@ -124,7 +130,7 @@ __global__ void __launch_bounds__(256) group_rmsnorm(const float* __restrict__ i
 // ---------------------------------------------------------------------------------------------------------------------
 // matrix products
 // ---------------------------------------------------------------------------------------------------------------------
-enum { HEPI_STORE = 0, HEPI_ADD = 1, HEPI_GLU = 2, HEPI_GELU_MUL = 3 };
+enum { HEPI_STORE = 0, HEPI_ADD = 1, HEPI_GLU = 2, HEPI_GELU_MUL = 3, HEPI_XIELU = 4 };
 
 struct GemmP {
   const float* A;          // activations, row pitch lda
@@ -133,6 +139,7 @@ struct GemmP {
   float* C;                // row pitch ldc
   int M, N, K, lda, ldw, ldc;
   long long sA, sW, sC;    // element strides per blockIdx.z (per-head batches); sW also is the stride between experts
+  int z_wdiv;              // batch z reads weight batch z / z_wdiv (query heads sharing one key / value head)
   const int* a_map;        // logical row i reads A row a_map[i] / a_div (null: row i)
   int a_div;
   const int* c_map;        // logical row i writes C row c_map[i] (null: row i)
@@ -146,12 +153,16 @@ struct GemmP {
   const void* aux;         // GELU_MUL: C = gelu_tanh(acc) * aux[aux_row[row] * aux_ld + aux_off + n]
   const int* aux_row;
   int aux_ld, aux_off;
+  const float* bias;       // [N], nullable: added to the accumulator before the epilogue
+  float act_a, act_b;      // XIELU: z > 0 ? act_a z^2 + z/2 : act_b (e^z - 1 - z) + z/2
 };
 
 template <typename WT, int EPI>
 __device__ __forceinline__ void gemm_epilogue(const GemmP& P, float* __restrict__ crow, int cr, int n, float v, float v2) {
+  if (P.bias) v += P.bias[n];
   if (EPI == HEPI_STORE) crow[n] = P.alpha * v;
   else if (EPI == HEPI_ADD) crow[n] += P.alpha * v;
+  else if (EPI == HEPI_XIELU) crow[n] = v > 0.f ? fmaf(P.act_a * v, v, 0.5f * v) : fmaf(P.act_b, expm1f(v) - v, 0.5f * v);
   else if (EPI == HEPI_GLU) {
     const float g = fminf(v, P.lim), u = fminf(fmaxf(v2, -P.lim), P.lim);
     crow[n] = g * sigmoid_f(1.702f * g) * (u + 1.f);
@@ -170,7 +181,7 @@ __global__ void __launch_bounds__(256) gemm_tiled(const GemmP P) {
   __shared__ __align__(16) float Bs[DUAL ? 2 : 1][BK][BN + 4];
   __shared__ int rowsA[BM], rowsC[BM];
   const int tid = threadIdx.x;
-  long long aoff = (long long)blockIdx.z * P.sA, woff = (long long)blockIdx.z * P.sW, coff = (long long)blockIdx.z * P.sC;
+  long long aoff = (long long)blockIdx.z * P.sA, woff = (long long)((int)blockIdx.z / P.z_wdiv) * P.sW, coff = (long long)blockIdx.z * P.sC;
   int row0, nrows;
   if (P.tiles) {
     if ((int)blockIdx.y >= *P.n_tiles) return;
@@ -292,7 +303,7 @@ __global__ void __launch_bounds__(256) gemm_mma(const GemmP P) {
   bf (*Bs)[BT][PITCH] = reinterpret_cast<bf (*)[BT][PITCH]>(smraw + (size_t)BM * PITCH * 2);   // [ST][BT][PITCH]
   __shared__ int rowsA[BM], rowsC[BM];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  long long aoff = (long long)blockIdx.z * P.sA, woff = (long long)blockIdx.z * P.sW, coff = (long long)blockIdx.z * P.sC;
+  long long aoff = (long long)blockIdx.z * P.sA, woff = (long long)((int)blockIdx.z / P.z_wdiv) * P.sW, coff = (long long)blockIdx.z * P.sC;
   int row0, nrows;
   if (P.tiles) {
     if ((int)blockIdx.y >= *P.n_tiles) return;
@@ -467,7 +478,7 @@ __global__ void __launch_bounds__(256) gemv_rows(const GemmP P) {
     aoff = woff = coff = 0;
     M = min(MR, P.z_rows - z * MR);
   } else {
-    aoff = (long long)z * P.sA; woff = (long long)z * P.sW; coff = (long long)z * P.sC;
+    aoff = (long long)z * P.sA; woff = (long long)(z / P.z_wdiv) * P.sW; coff = (long long)z * P.sC;
   }
   const int mbase = P.z_rows > 0 ? z * MR : 0;
   const WT* __restrict__ W = reinterpret_cast<const WT*>(P.W) + woff;
@@ -681,9 +692,16 @@ __global__ void __launch_bounds__(512) ssd_scan(const float* __restrict__ proj, 
 // scores, lane = latent channel (mod 32) for the weighted sum.  Online softmax in fp32.  With NS > 1 (few tokens: decoding) the
 // key range is cut into NS shares over blockIdx.z and latent_swa_merge combines the partial results.
 // ---------------------------------------------------------------------------------------------------------------------
+// first position that position i sees: mask 0 is a sliding window of `size` positions (i included), mask 1 cuts the sequence
+// into chunks of `size` positions counted from position 0, and i sees its own chunk up to itself
+__host__ __device__ __forceinline__ int mask_first(int mask, int size, int i) {
+  if (mask == 1) return (i / size) * size;
+  return i - size + 1 > 0 ? i - size + 1 : 0;
+}
+
 template <typename CT, int RV>
 __global__ void __launch_bounds__(256) latent_swa_attn(const float* __restrict__ qa, const CT* __restrict__ cache, float* __restrict__ out,
-                                                       int T, int H, int R, const int* __restrict__ ctl, int window, int ring,
+                                                       int T, int H, int R, const int* __restrict__ ctl, int mask, int window, int ring,
                                                        float scale, int TQ, int NS, float* __restrict__ part) {
   extern __shared__ float sm[];
   const int NW = 8, HB = NW / TQ;
@@ -695,8 +713,8 @@ __global__ void __launch_bounds__(256) latent_swa_attn(const float* __restrict__
   const int pos0 = ctl[0];
   for (int r = lane; r < R; r += 32) qs[w * R + r] = active ? qa[((size_t)t * H + h) * R + r] * scale : 0.f;
   const int i = pos0 + t;
-  const int lo_w = max(0, i - window + 1), hi_w = i;
-  int lo = max(0, pos0 + tq0 - window + 1), hi = pos0 + min(T, tq0 + TQ) - 1;
+  const int lo_w = mask_first(mask, window, i), hi_w = i;
+  int lo = mask_first(mask, window, pos0 + tq0), hi = pos0 + min(T, tq0 + TQ) - 1;
   if (NS > 1) {   // this CTA's share of the key range (whole tiles of 32)
     const int tiles = (hi - lo + 32) / 32, per = (tiles + NS - 1) / NS;
     const int lo_s = lo + (int)blockIdx.z * per * 32;
@@ -806,13 +824,13 @@ __global__ void pack_keys_values(const float* __restrict__ kf, const float* __re
   }
 }
 
-// S [H][Tq][Lk] in place: column c is position first + c, row t is position qpos0 + t; entries outside the window become 0
-__global__ void __launch_bounds__(128) softmax_band(float* __restrict__ S, int Tq, int Lk, int first, int qpos0, int window) {
+// S [H][Tq][Lk] in place: column c is position first + c, row t is position qpos0 + t; entries the mask hides become 0
+__global__ void __launch_bounds__(128) softmax_band(float* __restrict__ S, int Tq, int Lk, int first, int qpos0, int mask, int window) {
   __shared__ float red[33];
   const int t = blockIdx.x, h = blockIdx.y;
   float* row = S + ((size_t)h * Tq + t) * Lk;
   const int i = qpos0 + t;
-  const int c_lo = max(0, i - window + 1 - first), c_hi = i - first;   // inclusive
+  const int c_lo = max(0, mask_first(mask, window, i) - first), c_hi = i - first;   // inclusive
   float mx = -1e30f;
   for (int c = c_lo + (int)threadIdx.x; c <= c_hi; c += blockDim.x) mx = fmaxf(mx, row[c]);
   mx = warp_max(mx);
@@ -825,6 +843,219 @@ __global__ void __launch_bounds__(128) softmax_band(float* __restrict__ S, int T
   sum = block_sum(sum, red);
   const float inv = 1.f / sum;
   for (int c = threadIdx.x; c < Lk; c += blockDim.x) row[c] = (c >= c_lo && c <= c_hi) ? row[c] * inv : 0.f;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Layer norm with a weight and no bias: (x - mean) / sqrt(mean((x - mean)^2) + eps) * w per row of n values.
+// mode 0: out = result; mode 1: out += alpha * result (a normalised sublayer output added into the residual stream).
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) layer_norm(const float* __restrict__ in, int ld_in, const float* __restrict__ w,
+                                                  float* __restrict__ out, int ld_out, int n, float eps, int mode, float alpha) {
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const float* x = in + (size_t)t * ld_in;
+  float* o = out + (size_t)t * ld_out;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += x[i];
+  const float mean = block_sum(s, red) / (float)n;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) { const float d = x[i] - mean; ss = fmaf(d, d, ss); }
+  const float sc = 1.f / sqrtf(block_sum(ss, red) / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = (x[i] - mean) * sc * w[i];
+    o[i] = mode == 0 ? v : o[i] + alpha * v;
+  }
+}
+
+// x[t][:] += row[:] for the T rows of a step (the per-pass vector of a layer loop)
+__global__ void add_row(float* __restrict__ x, int ld, const float* __restrict__ row, int n) {
+  float* o = x + (size_t)blockIdx.x * ld;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] += row[i];
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Query / key preparation of grouped-query attention, one CTA per token of the step (position ctl[0] + t):
+//   q <- rot(q / rms(q) * qw),  k <- rot(k / rms(k) * kw)   with the RMS taken over the whole projection (all heads at once);
+//   rot acts on the first rot_dims dimensions of every head: the pair (2i, 2i + 1) turns by the angle pos * freq[i], and cos / sin
+//   are multiplied by `mag`.  Positions and angles are fp32.
+// q goes to q_out; the prepared key goes to row pos % ring of kcache.  Values: with v_src == nullptr the value of a position is
+// its key projection as projected (before norm and rotation); otherwise v_src rows (same pitch as k) are cached.
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) qk_norm_rope(const float* __restrict__ q, float* __restrict__ q_out, int HD,
+                                                    const float* __restrict__ k, const float* __restrict__ v_src, int GD, int GV,
+                                                    const float* __restrict__ qw, const float* __restrict__ kw, float eps, int D,
+                                                    int rot_dims, const float* __restrict__ freq, float mag,
+                                                    const int* __restrict__ ctl, float* __restrict__ kcache,
+                                                    float* __restrict__ vcache, int ring) {
+  __shared__ float red[33];
+  const int t = blockIdx.x, pos = ctl[0] + t;
+  const size_t row = (size_t)(pos % ring);
+  const float* qr = q + (size_t)t * HD;
+  const float* kr = k + (size_t)t * GD;
+  const float* vr = v_src ? v_src + (size_t)t * GV : kr;
+  float sq = 0.f, sk = 0.f;
+  for (int e = threadIdx.x; e < HD; e += blockDim.x) sq = fmaf(qr[e], qr[e], sq);
+  for (int e = threadIdx.x; e < GD; e += blockDim.x) sk = fmaf(kr[e], kr[e], sk);
+  const float nq = qw ? 1.f / sqrtf(block_sum(sq, red) / (float)HD + eps) : 1.f;
+  const float nk = kw ? 1.f / sqrtf(block_sum(sk, red) / (float)GD + eps) : 1.f;
+  const float fpos = (float)pos;
+  for (int e = threadIdx.x; e < HD + GD; e += blockDim.x) {
+    const bool isq = e < HD;
+    const int c = isq ? e : e - HD, d = c % D;
+    const float* src = isq ? qr : kr;
+    const float* w = isq ? qw : kw;
+    const float nrm = isq ? nq : nk;
+    float v = src[c] * nrm * (w ? w[c] : 1.f);
+    if (d < rot_dims) {
+      const int cp = c ^ 1;                                   // the other half of the pair (2i, 2i + 1)
+      const float u = src[cp] * nrm * (w ? w[cp] : 1.f);
+      const float a = fpos * freq[d >> 1];
+      const float cs = cosf(a) * mag, sn = sinf(a) * mag;
+      v = (d & 1) ? fmaf(v, cs, u * sn) : fmaf(v, cs, -u * sn);
+    }
+    if (isq) q_out[(size_t)t * HD + c] = v;
+    else kcache[row * GD + c] = v;
+  }
+  for (int e = threadIdx.x; e < GV; e += blockDim.x) vcache[row * GV + e] = vr[e];
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Grouped-query softmax attention for decode-sized steps: one CTA per (token, share of its keys), all heads in the CTA, because
+// the heads' scores may be mixed before the softmax:
+//   raw_g(i, j) = scale * q[i][g] . k[j][g / rep];   score_h = sum_g talk[h][g] raw_g   (talk null: score_h = raw_h);
+//   o[i][h] = sum_j softmax_j(score_h) v[j][h / rep]   over the positions j that the mask lets i see (mask_first(..) <= j <= i).
+// Keys [ring][G*D] and values [ring][G*Dv] are ring caches (position j in row j % ring).  Tiles of 32 keys are staged in shared
+// memory; warp w owns heads w, w + 8, ... with their running maximum, sum and weighted value sum in shared memory (online
+// softmax, fp32).  NS > 1: the key range is cut into NS shares over blockIdx.y, partial results {m, l, acc[Dv]} go to `part`
+// in the layout latent_swa_merge reads.
+// ---------------------------------------------------------------------------------------------------------------------
+__host__ __device__ inline size_t gqa_attn_smem_floats(int H, int G, int D, int Dv) {
+  return (size_t)H * D + (size_t)H * 32 + (size_t)32 * (G * D + 1) + 2 * (size_t)H + (size_t)H * Dv + (size_t)H * H + 8 * 32 + 32;
+}
+__global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc,
+                                                float* __restrict__ out, const float* __restrict__ talk, int T, int H, int G, int D,
+                                                int Dv, const int* __restrict__ ctl, int mask, int span, int ring, float scale, int NS,
+                                                float* __restrict__ part) {
+  extern __shared__ float sm[];
+  const int GD = G * D, GV = G * Dv, rep = H / G;
+  float* qs = sm;                              // [H][D]
+  float* sc = qs + (size_t)H * D;              // [H][32] raw scores of the tile
+  float* ks = sc + (size_t)H * 32;             // [32][GD + 1]
+  float* ms = ks + (size_t)32 * (GD + 1);      // [H] running maximum
+  float* ls = ms + H;                          // [H] running sum
+  float* accs = ls + H;                        // [H][Dv]
+  float* tk = accs + (size_t)H * Dv;           // [H][H]
+  float* ps = tk + (size_t)H * H;              // [8][32] weights of the warp's current head
+  int* rowoff = reinterpret_cast<int*>(ps + 8 * 32);   // [32] ring rows of the tile's keys
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int t = blockIdx.x, i = ctl[0] + t;
+  int lo = mask_first(mask, span, i), hi = i;
+  if (NS > 1) {   // this CTA's share of the key range (whole tiles of 32)
+    const int tiles = (hi - lo + 32) / 32, per = (tiles + NS - 1) / NS;
+    lo += (int)blockIdx.y * per * 32;
+    hi = min(hi, lo + per * 32 - 1);
+  }
+  for (int e = tid; e < H * D; e += blockDim.x) qs[e] = q[(size_t)t * H * D + e];
+  for (int e = tid; e < H; e += blockDim.x) { ms[e] = -1e30f; ls[e] = 0.f; }
+  for (int e = tid; e < H * Dv; e += blockDim.x) accs[e] = 0.f;
+  if (talk) for (int e = tid; e < H * H; e += blockDim.x) tk[e] = talk[e];
+  for (int j0 = lo; j0 <= hi; j0 += 32) {
+    __syncthreads();
+    if (tid < 32) rowoff[tid] = (j0 + tid) % ring;
+    for (int e = tid; e < 32 * GD; e += blockDim.x) {
+      const int jj = e / GD, r = e - jj * GD, j = j0 + jj;
+      ks[jj * (GD + 1) + r] = j <= hi ? kc[(size_t)(j % ring) * GD + r] : 0.f;
+    }
+    __syncthreads();
+    for (int h = w; h < H; h += 8) {   // raw scores: lane = key
+      const float* kr = ks + lane * (GD + 1) + (h / rep) * D;
+      const float* qr = qs + h * D;
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      int d = 0;
+      for (; d + 4 <= D; d += 4) {
+        s0 = fmaf(qr[d], kr[d], s0); s1 = fmaf(qr[d + 1], kr[d + 1], s1);
+        s2 = fmaf(qr[d + 2], kr[d + 2], s2); s3 = fmaf(qr[d + 3], kr[d + 3], s3);
+      }
+      for (; d < D; d++) s0 = fmaf(qr[d], kr[d], s0);
+      sc[h * 32 + lane] = ((s0 + s1) + (s2 + s3)) * scale;
+    }
+    __syncthreads();
+    const bool valid = j0 + lane <= hi;
+    for (int h = w; h < H; h += 8) {
+      float s;
+      if (talk) {
+        s = 0.f;
+        for (int g = 0; g < H; g++) s = fmaf(tk[h * H + g], sc[g * 32 + lane], s);
+      } else s = sc[h * 32 + lane];
+      s = valid ? s : -1e30f;
+      const float m_old = ms[h];
+      const float m_new = fmaxf(m_old, warp_max(s));
+      const float corr = expf(m_old - m_new);
+      const float p = valid ? expf(s - m_new) : 0.f;
+      const float l = ls[h] * corr + warp_sum(p);
+      ps[w * 32 + lane] = p;
+      __syncwarp();
+      const float* vb = vc + (size_t)(h / rep) * Dv;
+      for (int r = lane; r < Dv; r += 32) {
+        float a = accs[h * Dv + r] * corr;
+        for (int jj = 0; jj < 32; jj++) {
+          const float pj = ps[w * 32 + jj];
+          if (pj != 0.f) a = fmaf(pj, vb[(size_t)rowoff[jj] * GV + r], a);
+        }
+        accs[h * Dv + r] = a;
+      }
+      __syncwarp();
+      if (lane == 0) { ms[h] = m_new; ls[h] = l; }
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+  for (int h = w; h < H; h += 8) {
+    if (NS > 1) {
+      float* pp = part + (((size_t)t * H + h) * NS + blockIdx.y) * (Dv + 2);
+      if (lane == 0) { pp[0] = ms[h]; pp[1] = ls[h]; }
+      for (int r = lane; r < Dv; r += 32) pp[2 + r] = accs[h * Dv + r];
+    } else {
+      const float inv = 1.f / ls[h];
+      for (int r = lane; r < Dv; r += 32) out[((size_t)t * H + h) * Dv + r] = accs[h * Dv + r] * inv;
+    }
+  }
+}
+
+// Portions run the same attention as matrix products per block of queries (like the latent attention above).  pack_ring_kv
+// gathers the visible positions first .. first + Lk - 1 from the ring caches into per-group operands: keys [G][Lk][D], values
+// transposed [G][Dv][Lk].  mix_heads applies the heads' score mixing to a [H][Tq][Lk] score array (out of place).
+template <typename WT>
+__global__ void pack_ring_kv(const float* __restrict__ kc, const float* __restrict__ vc, WT* __restrict__ kb, WT* __restrict__ vt,
+                             int first, int Lk, int ring, int G, int D, int Dv) {
+  const int j = blockIdx.x;
+  const size_t row = (size_t)((first + j) % ring);
+  for (int e = threadIdx.x; e < G * D; e += blockDim.x) {
+    const int g = e / D, d = e - g * D;
+    kb[((size_t)g * Lk + j) * D + d] = from_f<WT>(kc[row * G * D + e]);
+  }
+  for (int e = threadIdx.x; e < G * Dv; e += blockDim.x) {
+    const int g = e / Dv, v = e - g * Dv;
+    vt[((size_t)g * Dv + v) * Lk + j] = from_f<WT>(vc[row * G * Dv + e]);
+  }
+}
+
+// out[h][e] = sum_g talk[h][g] in[g][e] for the n = Tq * Lk entries of every head; a CTA takes 128 consecutive entries
+__global__ void __launch_bounds__(128) mix_heads(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ talk,
+                                                 int H, long long n) {
+  extern __shared__ float sm[];
+  float* tk = sm;              // [H][H]
+  float* col = sm + H * H;     // [H][128]
+  const long long e = (long long)blockIdx.x * 128 + threadIdx.x;
+  for (int k = threadIdx.x; k < H * H; k += blockDim.x) tk[k] = talk[k];
+  if (e < n) for (int g = 0; g < H; g++) col[g * 128 + threadIdx.x] = in[(size_t)g * n + e];
+  __syncthreads();
+  if (e >= n) return;
+  for (int h = 0; h < H; h++) {
+    float s = 0.f;
+    for (int g = 0; g < H; g++) s = fmaf(tk[h * H + g], col[g * 128 + threadIdx.x], s);
+    out[(size_t)h * n + e] = s;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -885,12 +1116,12 @@ __global__ void __launch_bounds__(1024) moe_plan(const int* __restrict__ idx, in
 }
 
 __global__ void moe_combine(float* __restrict__ x, int ldx, const float* __restrict__ y, const float* __restrict__ wgt, int top,
-                            int width, float alpha) {
+                            int width, float alpha, int add) {
   const int t = blockIdx.x;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float s = 0.f;
     for (int k = 0; k < top; k++) s = fmaf(wgt[(size_t)t * top + k], y[((size_t)t * top + k) * width + c], s);
-    x[(size_t)t * ldx + c] += alpha * s;
+    x[(size_t)t * ldx + c] = add ? x[(size_t)t * ldx + c] + alpha * s : alpha * s;
   }
 }
 

@@ -3,13 +3,19 @@
 // dsk_forward / dsk_forward_chunk / dsk_decode_greedy drive.  Included at the end of dsk_engine.cu (it uses that file's error,
 // allocation and sampling helpers); dsk_model::hy / dsk_state::hy point at the structures below.
 //
-// Tensor names (safetensors, [out, in] matrices):  embed, side.embed, final.norm, and per layer i ("l<i>."):
-//   norm1 | mix.in, mix.conv, mix.conv.b, mix.dt_bias, mix.A_log, mix.D, mix.norm, mix.o              (state-space mixer)
+// Tensor names (safetensors, [out, in] matrices):  embed, side.embed, final.norm, head (untied LM head), loop.step (layer loop),
+// and per layer i ("l<i>."):
+//   norm1 (and norm1b, norm2, norm2b in sandwich blocks)
+//         | mix.in, mix.conv, mix.conv.b, mix.dt_bias, mix.A_log, mix.D, mix.norm, mix.o              (state-space mixer)
 //         | mix.q, mix.dkv, mix.dkv.norm, mix.uk, mix.uv, mix.o                                        (latent attention)
+//         | mix.q, mix.k, mix.q.norm, mix.k.norm, mix.talk, mix.o                                      (grouped-query attention)
 //   mlp.router, mlp.correction, mlp.e<j>.gate|up|down                                                 (routed feed-forward)
+//   mlp.up, mlp.up.b, mlp.down, mlp.down.b, mlp.act                                                   (dense feed-forward)
 //   side.gate, side.proj, side.norm                                                                   (per-layer token input)
-// A layer computes, with h = norm1(x):  x += m (mixer(h) + ff(h));  then, when the model has a per-layer token table,
+// A parallel block computes, with h = norm1(x):  x += m (mixer(h) + ff(h));  a sandwich block  x += norm1b(mixer(norm1(x))),
+// x += norm2b(ff(norm2(x))).  Then, when the model has a per-layer token table,
 // g = gelu_tanh(side.gate x) * side.embed[token][i*sd : (i+1)*sd],  y = side.proj g,  x += m * rmsnorm(y) * side.norm.
+// A layer loop repeats a range of layers with the same weights; every repeat ("layer run") has its own cache / state.
 #pragma once
 
 namespace hyb {
@@ -24,7 +30,7 @@ struct HTensor {
 
 struct HLayer {
   dsk_layer_spec sp;
-  float* norm1 = nullptr;
+  float *norm1 = nullptr, *norm1b = nullptr, *norm2 = nullptr, *norm2b = nullptr;
   // state-space mixer
   HTensor in, o;
   float *conv_w = nullptr, *conv_b = nullptr, *dt_bias = nullptr, *A_log = nullptr, *D = nullptr, *mnorm = nullptr;
@@ -34,6 +40,14 @@ struct HLayer {
   float* dkv_norm = nullptr;
   int owner = -1;                   // layer whose latent cache this layer reads (itself unless kv_from)
   int ring = 0;                     // rows of this layer's own ring cache (owners only)
+  // grouped-query attention (with q, o above): key projection, whole-projection norm weights, score mixing, rotation table
+  HTensor kproj;
+  float *q_norm = nullptr, *k_norm = nullptr, *talk = nullptr, *rot_freq = nullptr;
+  float rot_mag = 1.f;
+  // dense feed-forward
+  HTensor up, down;
+  float *up_b = nullptr, *down_b = nullptr, *act = nullptr;
+  float act_a = 0.f, act_b = 0.f;
   // routed feed-forward
   HTensor gate_s, up_s, down_s;     // expert stacks [E][ff][width], [E][ff][width], [E][width][ff]
   std::vector<char> have;           // 3 E flags
@@ -43,19 +57,28 @@ struct HLayer {
   float* snorm = nullptr;
 };
 
+// one execution of a layer: layers inside the loop range run once per pass, each time with a state of their own
+struct Run {
+  int layer;
+  int pass;        // >= 0: this run opens pass `pass` of the loop (loop.step[pass] is added to the residual stream first)
+  int owner_run;   // latent attention: the run whose latent cache this run reads (itself unless kv_from)
+};
+
 struct Model {
   dsk_hybrid_config c;
   std::vector<HLayer> L;
-  HTensor embed, side_embed;
-  float* final_norm = nullptr;
+  std::vector<Run> runs;
+  HTensor embed, side_embed, head;
+  float *final_norm = nullptr, *loop_step = nullptr;
   size_t wsize = 4;                 // bytes per matrix element
 };
 
 struct LayerState {
   float* ssm = nullptr;             // [heads][vdim][state]
   float* hist = nullptr;            // [conv - 1][channels]
-  void* cache = nullptr;            // [ring][kv_rank] (owner layers)
-  size_t ssm_bytes = 0, hist_bytes = 0, cache_bytes = 0;
+  void* cache = nullptr;            // [ring][kv_rank] (owner layers); grouped-query attention: keys [ring][kv_heads * dim]
+  void* vcache = nullptr;           // grouped-query attention: values [ring][kv_heads * vdim]
+  size_t ssm_bytes = 0, hist_bytes = 0, cache_bytes = 0, vcache_bytes = 0;
 };
 
 struct State {
@@ -68,10 +91,11 @@ struct State {
   int head_rows = 0;                         // rows of the logits buffer: the LM head runs over the wanted rows in groups of this size
   float* part = nullptr;                     // partial softmax results of key-split attention (decode-sized chunks)
   // prefill attention as matrix products (blocks of kPrefillQ queries): up-projected keys / values, their per-head packing, scores
-  float *kf = nullptr, *vf = nullptr, *sc = nullptr;
+  float *kf = nullptr, *vf = nullptr, *sc = nullptr, *sc2 = nullptr;   // sc2: scores after the heads were mixed
   void *kb = nullptr, *vt = nullptr;
   int* d_rows = nullptr;
   int prefill_keys = 0;                      // keys a block of queries can see at most; 0: the matrix path is off
+  float* y = nullptr;                        // a sublayer's output before its closing norm (sandwich blocks)
   float *x = nullptr, *h = nullptr, *b0 = nullptr, *b1 = nullptr, *b2 = nullptr, *b3 = nullptr, *wgt = nullptr, *logits = nullptr;
   int *h_tok = nullptr, *h_want = nullptr;   // pinned staging of a chunk's token ids / wanted rows
   std::vector<void*> allocs;
@@ -98,6 +122,10 @@ static int validate(const dsk_hybrid_config& c, const dsk_layer_spec* L) {
   if (c.norm_groups <= 0 || c.dim % c.norm_groups != 0) return fail(-1, "norm groups %d do not divide width %d", c.norm_groups, c.dim);
   if (c.chunk < 1 || c.chunk > 4096) return fail(-1, "chunk %d out of range (1..4096)", c.chunk);
   if (c.side_dim < 0) return fail(-1, "negative side_dim");
+  if (c.block != DSK_BLOCK_PARALLEL && c.block != DSK_BLOCK_SANDWICH) return fail(-1, "unknown block kind %d", c.block);
+  if (c.norm_kind != DSK_NORM_RMS && c.norm_kind != DSK_NORM_LAYER) return fail(-1, "unknown norm kind %d", c.norm_kind);
+  if (c.loop_times > 1 && (c.loop_start < 0 || c.loop_stop > c.n_layers || c.loop_start > c.loop_stop))
+    return fail(-1, "layer loop %d..%d outside the %d layers", c.loop_start, c.loop_stop, c.n_layers);
   for (int i = 0; i < c.n_layers; i++) {
     const dsk_layer_spec& s = L[i];
     if (s.mixer == DSK_MIX_SSD) {
@@ -115,8 +143,20 @@ static int validate(const dsk_hybrid_config& c, const dsk_layer_spec* L) {
         if (j >= i || L[j].mixer != DSK_MIX_LATENT_SWA || L[j].att_kv_from >= 0 || L[j].att_kv_rank != s.att_kv_rank)
           return fail(-1, "layer %d: kv_from %d must name an earlier latent-attention layer that projects its own latent of the same rank", i, j);
       }
+    } else if (s.mixer == DSK_MIX_GQA) {
+      if (s.att_heads <= 0 || s.att_kv_heads <= 0 || s.att_dim <= 0 || s.att_vdim <= 0 || s.att_window <= 0) return fail(-1, "layer %d: bad attention sizes", i);
+      if (s.att_heads % s.att_kv_heads != 0) return fail(-1, "layer %d: heads %d not a multiple of kv_heads %d", i, s.att_heads, s.att_kv_heads);
+      if (s.att_vdim != s.att_dim) return fail(-1, "layer %d: the values are the key projection, so vdim %d must equal dim %d", i, s.att_vdim, s.att_dim);
+      if (s.rot_dims < 0 || s.rot_dims > s.att_dim || s.rot_dims % 2 != 0) return fail(-1, "layer %d: rot dims %d must be even and at most dim %d", i, s.rot_dims, s.att_dim);
+      if (s.rot_dims > 0 && !(s.rot_base > 0.f)) return fail(-1, "layer %d: bad rotation base", i);
+      if (gqa_attn_smem_floats(s.att_heads, s.att_kv_heads, s.att_dim, s.att_vdim) * 4 > 200 * 1024)
+        return fail(-1, "layer %d: %d heads x %d with %d key heads do not fit the attention kernel's shared memory", i, s.att_heads, s.att_dim, s.att_kv_heads);
     } else return fail(-1, "layer %d: unknown mixer %d", i, s.mixer);
-    if (s.ff_kind == DSK_FF_MOE) {
+    if (s.mixer != DSK_MIX_SSD && s.att_mask != DSK_MASK_WINDOW && s.att_mask != DSK_MASK_CHUNK) return fail(-1, "layer %d: unknown mask %d", i, s.att_mask);
+    if (s.ff_kind == DSK_FF_DENSE) {
+      if (s.ff_hidden <= 0) return fail(-1, "layer %d: bad feed-forward size", i);
+      if (s.ff_act != DSK_ACT_XIELU) return fail(-1, "layer %d: unknown activation %d", i, s.ff_act);
+    } else if (s.ff_kind == DSK_FF_MOE) {
       if (s.ff_experts <= 0 || s.ff_top <= 0 || s.ff_top > s.ff_experts || s.ff_hidden <= 0) return fail(-1, "layer %d: bad routed feed-forward sizes", i);
       if (s.ff_experts > 4096) return fail(-1, "layer %d: more than 4096 experts unsupported", i);
     } else if (s.ff_kind != DSK_FF_NONE) return fail(-1, "layer %d: unknown feed-forward kind %d", i, s.ff_kind);
@@ -139,6 +179,9 @@ static void set_kernel_attrs() {
   cudaFuncSetAttribute(gemm_mma<HEPI_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
   cudaFuncSetAttribute(gemm_mma<HEPI_GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
   cudaFuncSetAttribute(gemm_mma<HEPI_GELU_MUL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
+  cudaFuncSetAttribute(gemm_mma<HEPI_XIELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
+  cudaFuncSetAttribute(gqa_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(mix_heads, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   done = true;
 }
 
@@ -162,14 +205,57 @@ static dsk_model* model_create(const dsk_hybrid_config* cfg, const dsk_layer_spe
     L.sp = layers[i];
     if (L.sp.ff_kind == DSK_FF_MOE) L.have.assign(3 * (size_t)L.sp.ff_experts, 0);
     if (L.sp.mixer == DSK_MIX_LATENT_SWA) L.owner = L.sp.att_kv_from >= 0 ? L.sp.att_kv_from : i;
+    if (L.sp.mixer == DSK_MIX_GQA) L.owner = i;
   }
-  // ring caches: the owner keeps the widest window among its readers plus one chunk, capped by the sequence limit
+  // ring caches: the owner keeps the widest window (or chunk of the mask) among its readers plus one step, capped by the sequence limit
   for (int i = 0; i < cfg->n_layers; i++) {
     const HLayer& L = M->L[i];
-    if (L.sp.mixer != DSK_MIX_LATENT_SWA) continue;
+    if (L.owner < 0) continue;
     HLayer& O = M->L[L.owner];
     const long long need = (long long)L.sp.att_window - 1 + cfg->chunk;
     O.ring = (int)std::max<long long>(O.ring, std::min<long long>(need, (long long)cfg->max_seq_len));
+  }
+  // the order of layer runs: layers before the loop, the loop's passes, the layers after it
+  const bool looped = cfg->loop_times > 1 && cfg->loop_stop > cfg->loop_start;
+  const int ls = looped ? cfg->loop_start : 0, le = looped ? cfg->loop_stop : 0, lt = looped ? cfg->loop_times : 0;
+  for (int i = 0; i < ls; i++) M->runs.push_back(Run{i, -1, -1});
+  for (int t = 0; t < lt; t++)
+    for (int i = ls; i < le; i++) M->runs.push_back(Run{i, i == ls ? t : -1, -1});
+  for (int i = le; i < cfg->n_layers; i++) M->runs.push_back(Run{i, -1, -1});
+  for (size_t r = 0; r < M->runs.size(); r++) {   // a reader of another layer's latent cache reads that layer's latest run
+    const int o = M->L[M->runs[r].layer].owner;
+    if (o < 0) continue;
+    for (int q = (int)r; q >= 0; q--)
+      if (M->runs[q].layer == o) { M->runs[r].owner_run = q; break; }
+    if (M->runs[r].owner_run < 0) { fail(-1, "layer %d reads the latent cache of layer %d, which has not run before it", M->runs[r].layer, o); dsk_model_destroy(m); return nullptr; }
+  }
+  // rotation tables of the grouped-query attention layers: frequency per pair, in double, rounded once to fp32
+  for (int i = 0; i < cfg->n_layers; i++) {
+    HLayer& L = M->L[i];
+    const dsk_layer_spec& s = L.sp;
+    if (s.mixer != DSK_MIX_GQA || s.rot_dims <= 0) continue;
+    const int half = s.rot_dims / 2;
+    std::vector<float> f((size_t)half);
+    const double base = s.rot_base, dims = s.rot_dims;
+    const bool yarn = s.rot_factor > 0.f;
+    double lo = 0, hi = 0;
+    if (yarn) {   // the pair index at which `original` positions hold t turns
+      auto at = [&](double t) { return dims * std::log((double)s.rot_original / (2.0 * M_PI * t)) / (2.0 * std::log(base)); };
+      lo = std::max(std::floor(at(s.rot_fast)), 0.0);
+      hi = std::min(std::ceil(at(s.rot_slow)), dims - 1.0);
+      L.rot_mag = (float)(0.1 * std::log((double)s.rot_factor) + 1.0);
+    }
+    for (int k = 0; k < half; k++) {
+      double fr = std::pow(base, -2.0 * k / dims);
+      if (yarn) {
+        const double ramp = std::min(1.0, std::max(0.0, (k - lo) / std::max(hi - lo, 0.001)));
+        fr = fr / s.rot_factor * ramp + fr * (1.0 - ramp);
+      }
+      f[k] = (float)fr;
+    }
+    if (dmalloc(m, (void**)&L.rot_freq, (size_t)half * 4) || cudaMemcpy(L.rot_freq, f.data(), (size_t)half * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+      fail(-2, "rotation table allocation failed"); dsk_model_destroy(m); return nullptr;
+    }
   }
   return m;
 }
@@ -228,6 +314,14 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
   };
   if (nm == "embed") return MAT(M->embed, c.vocab_size, c.dim);
   if (nm == "final.norm") return F32(&M->final_norm, c.dim, 0);
+  if (nm == "head") {
+    if (c.tie_head) return fail(-4, "tensor %s: this model's LM head is its embedding table", name);
+    return MAT(M->head, c.vocab_size, c.dim);
+  }
+  if (nm == "loop.step") {
+    if (c.loop_times <= 1) return fail(-4, "tensor %s: the model has no layer loop", name);
+    return F32(&M->loop_step, c.loop_times, c.dim);
+  }
   if (nm == "side.embed") {
     if (c.side_dim <= 0) return fail(-4, "tensor %s: the model has no per-layer token input", name);
     return MAT(M->side_embed, c.vocab_size, (long long)c.side_dim * c.n_layers);
@@ -240,6 +334,11 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
   const dsk_layer_spec& s = L.sp;
   const std::string rest(end + 1);
   if (rest == "norm1") return F32(&L.norm1, c.dim, 0);
+  if (c.block == DSK_BLOCK_SANDWICH) {
+    if (rest == "norm1b") return F32(&L.norm1b, c.dim, 0);
+    if (rest == "norm2" && s.ff_kind != DSK_FF_NONE) return F32(&L.norm2, c.dim, 0);
+    if (rest == "norm2b" && s.ff_kind != DSK_FF_NONE) return F32(&L.norm2b, c.dim, 0);
+  }
   if (rest.rfind("mix.", 0) == 0) {
     const std::string k = rest.substr(4);
     if (is_ssd(s)) {
@@ -252,6 +351,14 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
       if (k == "D") return F32(&L.D, s.ssm_heads, 0);
       if (k == "norm") return F32(&L.mnorm, inner, 0);
       if (k == "o") return MAT(L.o, c.dim, inner);
+    } else if (s.mixer == DSK_MIX_GQA) {
+      const long long HD = (long long)s.att_heads * s.att_dim, GD = (long long)s.att_kv_heads * s.att_dim;
+      if (k == "q") return MAT(L.q, HD, c.dim);
+      if (k == "k") return MAT(L.kproj, GD, c.dim);
+      if (k == "q.norm") return F32(&L.q_norm, HD, 0);
+      if (k == "k.norm") return F32(&L.k_norm, GD, 0);
+      if (k == "talk" && s.att_talk) return F32(&L.talk, s.att_heads, s.att_heads);
+      if (k == "o") return MAT(L.o, c.dim, (long long)s.att_heads * s.att_vdim);
     } else {
       const long long H = s.att_heads;
       if (k == "q") return MAT(L.q, H * s.att_dim, c.dim);
@@ -264,6 +371,23 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
       }
     }
     return fail(-4, "unknown tensor name %s for this layer's mixer", name);
+  }
+  if (rest.rfind("mlp.", 0) == 0 && s.ff_kind == DSK_FF_DENSE) {
+    const std::string k = rest.substr(4);
+    if (k == "up") return MAT(L.up, s.ff_hidden, c.dim);
+    if (k == "up.b") return F32(&L.up_b, s.ff_hidden, 0);
+    if (k == "down") return MAT(L.down, c.dim, s.ff_hidden);
+    if (k == "down.b") return F32(&L.down_b, c.dim, 0);
+    if (k == "act") {   // the activation's two numbers enter as softplus(p) and 1/2 + softplus(q), in fp32
+      if (int rc = F32(&L.act, 2, 0)) return rc;
+      float pq[2];
+      CK(cudaMemcpy(pq, L.act, sizeof(pq), cudaMemcpyDeviceToHost));
+      auto softplus = [](float v) { return v > 20.f ? v : log1pf(expf(v)); };
+      L.act_a = softplus(pq[0]);
+      L.act_b = 0.5f + softplus(pq[1]);
+      return 0;
+    }
+    return fail(-4, "unknown tensor name %s", name);
   }
   if (rest.rfind("mlp.", 0) == 0 && s.ff_kind == DSK_FF_MOE) {
     const std::string k = rest.substr(4);
@@ -305,17 +429,26 @@ static int finalize(dsk_model* m) {
   if (!M->embed.present) return fail(-5, "missing tensor embed");
   if (!M->final_norm) return fail(-5, "missing tensor final.norm");
   if (c.side_dim > 0 && !M->side_embed.present) return fail(-5, "missing tensor side.embed");
+  if (!c.tie_head && !M->head.present) return fail(-5, "missing tensor head");
+  if (c.loop_times > 1 && !M->loop_step) return fail(-5, "missing tensor loop.step");
   for (int i = 0; i < c.n_layers; i++) {
     HLayer& L = M->L[i];
     const dsk_layer_spec& s = L.sp;
     if (!L.norm1) return fail(-5, "missing tensor l%d.norm1", i);
-    if (is_ssd(s)) {
+    if (c.block == DSK_BLOCK_SANDWICH && (!L.norm1b || (s.ff_kind != DSK_FF_NONE && (!L.norm2 || !L.norm2b))))
+      return fail(-5, "layer %d: missing norm tensors (norm1b, norm2, norm2b)", i);
+    if (s.mixer == DSK_MIX_GQA) {
+      if (!L.q.present || !L.kproj.present || !L.o.present || !L.q_norm || !L.k_norm || (s.att_talk && !L.talk))
+        return fail(-5, "layer %d: missing attention tensors (mix.q, k, q.norm, k.norm, talk, o)", i);
+    } else if (is_ssd(s)) {
       if (!L.in.present || !L.o.present || !L.conv_w || !L.conv_b || !L.dt_bias || !L.A_log || !L.D || !L.mnorm)
         return fail(-5, "layer %d: missing state-space mixer tensors (mix.in, conv, conv.b, dt_bias, A_log, D, norm, o)", i);
     } else {
       if (!L.q.present || !L.ukT.present || !L.uk.present || !L.uv.present || !L.o.present) return fail(-5, "layer %d: missing latent-attention tensors (mix.q, uk, uv, o)", i);
       if (s.att_kv_from < 0 && (!L.dkv.present || !L.dkv_norm)) return fail(-5, "layer %d: missing mix.dkv / mix.dkv.norm", i);
     }
+    if (s.ff_kind == DSK_FF_DENSE && (!L.up.present || !L.down.present || !L.up_b || !L.down_b || !L.act))
+      return fail(-5, "layer %d: missing feed-forward tensors (mlp.up, up.b, down, down.b, act)", i);
     if (s.ff_kind == DSK_FF_MOE) {
       if (!L.router || !L.correction) return fail(-5, "layer %d: missing mlp.router / mlp.correction", i);
       for (size_t k = 0; k < L.have.size(); k++)
@@ -333,15 +466,23 @@ static double active_bytes(const dsk_model* m) {
   const dsk_hybrid_config& c = M->c;
   const double ws = (double)M->wsize, W = c.dim;
   double tot = W * ws + (double)c.vocab_size * W * ws + W * 4;
-  for (const HLayer& L : M->L) {
+  for (const Run& R : M->runs) {
+    const HLayer& L = M->L[R.layer];
     const dsk_layer_spec& s = L.sp;
     double mat = 0, f32 = W;
-    if (is_ssd(s)) { mat += (double)ssd_proj(s) * W + W * ssd_inner(s); f32 += (double)ssd_channels(s) * (s.ssm_conv + 1) + 3.0 * s.ssm_heads + ssd_inner(s); }
+    if (R.pass >= 0) f32 += W;
+    if (c.block == DSK_BLOCK_SANDWICH) f32 += W * (s.ff_kind != DSK_FF_NONE ? 3 : 1);
+    if (s.mixer == DSK_MIX_GQA) {
+      const double HD = (double)s.att_heads * s.att_dim, GD = (double)s.att_kv_heads * s.att_dim;
+      mat += (HD + GD) * W + W * s.att_heads * s.att_vdim;
+      f32 += HD + GD + (s.att_talk ? (double)s.att_heads * s.att_heads : 0.0);
+    } else if (is_ssd(s)) { mat += (double)ssd_proj(s) * W + W * ssd_inner(s); f32 += (double)ssd_channels(s) * (s.ssm_conv + 1) + 3.0 * s.ssm_heads + ssd_inner(s); }
     else {
       mat += (double)s.att_heads * s.att_dim * W + (double)s.att_heads * (s.att_dim + s.att_vdim) * s.att_kv_rank + W * s.att_heads * s.att_vdim;
       if (s.att_kv_from < 0) { mat += (double)s.att_kv_rank * W; f32 += s.att_kv_rank; }
     }
     if (s.ff_kind == DSK_FF_MOE) { mat += 3.0 * s.ff_top * s.ff_hidden * W; f32 += (double)s.ff_experts * (W + 1); }
+    if (s.ff_kind == DSK_FF_DENSE) { mat += 2.0 * s.ff_hidden * W; f32 += s.ff_hidden + W; }
     if (c.side_dim > 0) { mat += 2.0 * c.side_dim * W + c.side_dim; f32 += W; }
     tot += mat * ws + f32 * 4;
   }
@@ -352,10 +493,15 @@ static double active_bytes(const dsk_model* m) {
 static int launches_per_token(const dsk_model* m) {
   const Model* M = m->hy;
   int n = 4;
-  for (const HLayer& L : M->L) {
+  const bool sandwich = M->c.block == DSK_BLOCK_SANDWICH;
+  for (const Run& R : M->runs) {
+    const HLayer& L = M->L[R.layer];
     const dsk_layer_spec& s = L.sp;
-    n += 1 + (is_ssd(s) ? 5 + (s.ssm_conv > 1 ? 1 : 0) : 5 + (s.att_kv_from < 0 ? 2 : 0));
+    n += 1 + (R.pass >= 0 ? 1 : 0) + (sandwich ? 1 + (s.ff_kind != DSK_FF_NONE ? 2 : 0) : 0);
+    if (s.mixer == DSK_MIX_GQA) n += 6;   // q, k, norm + rotation, attention, merge, o
+    else n += is_ssd(s) ? 5 + (s.ssm_conv > 1 ? 1 : 0) : 5 + (s.att_kv_from < 0 ? 2 : 0);
     if (s.ff_kind == DSK_FF_MOE) n += 5;
+    if (s.ff_kind == DSK_FF_DENSE) n += 2;
     if (M->c.side_dim > 0) n += 3;
   }
   return n;
@@ -377,6 +523,7 @@ static int state_reset(dsk_state* s) {
     if (l.ssm) CK(cudaMemsetAsync(l.ssm, 0, l.ssm_bytes, s->stream));
     if (l.hist) CK(cudaMemsetAsync(l.hist, 0, l.hist_bytes, s->stream));
     if (l.cache) CK(cudaMemsetAsync(l.cache, 0, l.cache_bytes, s->stream));
+    if (l.vcache) CK(cudaMemsetAsync(l.vcache, 0, l.vcache_bytes, s->stream));
   }
   S->next_pos = 0;
   s->last_pos = -1;
@@ -407,19 +554,29 @@ static dsk_state* state_create(dsk_model* m) {
   cudaEventCreate(&s->ev0); cudaEventCreate(&s->ev1);
   if (cudaGetLastError() != cudaSuccess) { fail(-2, "state allocation failed"); return nullptr; }
   size_t mx0 = c.dim, mx1 = c.dim, mx2 = c.dim, mx3 = c.dim, mxE = 1, mxTop = 1;
-  S->L.resize(c.n_layers);
-  for (int i = 0; i < c.n_layers; i++) {
+  S->L.resize(M->runs.size());   // one state per layer run
+  bool any_talk = false;
+  for (size_t r = 0; r < M->runs.size(); r++) {
+    const int i = M->runs[r].layer;
     const HLayer& L = M->L[i];
     const dsk_layer_spec& sp = L.sp;
-    LayerState& ls = S->L[i];
-    if (is_ssd(sp)) {
+    LayerState& ls = S->L[r];
+    if (sp.mixer == DSK_MIX_GQA) {
+      const size_t HD = (size_t)sp.att_heads * sp.att_dim, GD = (size_t)sp.att_kv_heads * sp.att_dim, GV = (size_t)sp.att_kv_heads * sp.att_vdim;
+      ls.cache_bytes = (size_t)L.ring * GD * 4;
+      ls.vcache_bytes = (size_t)L.ring * GV * 4;
+      if (salloc(S, &ls.cache, ls.cache_bytes) || salloc(S, &ls.vcache, ls.vcache_bytes)) return nullptr;
+      mx0 = std::max<size_t>(mx0, HD); mx1 = std::max<size_t>(mx1, GD); mx2 = std::max<size_t>(mx2, HD);
+      mx3 = std::max<size_t>(mx3, (size_t)sp.att_heads * sp.att_vdim);
+      any_talk |= sp.att_talk != 0;
+    } else if (is_ssd(sp)) {
       ls.ssm_bytes = (size_t)sp.ssm_heads * sp.ssm_vdim * sp.ssm_state * 4;
       ls.hist_bytes = (size_t)std::max(1, sp.ssm_conv - 1) * ssd_channels(sp) * 4;
       if (salloc(S, (void**)&ls.ssm, ls.ssm_bytes) || salloc(S, (void**)&ls.hist, ls.hist_bytes)) return nullptr;
       mx0 = std::max<size_t>(mx0, ssd_proj(sp)); mx1 = std::max<size_t>(mx1, ssd_channels(sp));
       mx2 = std::max<size_t>(mx2, ssd_inner(sp)); mx3 = std::max<size_t>(mx3, ssd_inner(sp));
     } else {
-      if (L.owner == i) {
+      if (M->runs[r].owner_run == (int)r) {
         ls.cache_bytes = (size_t)L.ring * sp.att_kv_rank * 4;
         if (salloc(S, &ls.cache, ls.cache_bytes)) return nullptr;
       }
@@ -433,31 +590,41 @@ static dsk_state* state_create(dsk_model* m) {
       mx0 = std::max<size_t>(mx0, sp.ff_experts);
       mx2 = std::max<size_t>(mx2, (size_t)sp.ff_top * sp.ff_hidden); mx3 = std::max<size_t>(mx3, (size_t)sp.ff_top * c.dim);
     }
+    if (sp.ff_kind == DSK_FF_DENSE) mx2 = std::max<size_t>(mx2, sp.ff_hidden);
     mx1 = std::max<size_t>(mx1, c.side_dim);
   }
   S->max_tiles = (int)(Tc * mxTop / 64 + mxE + 1);
   int rc = 0;
   size_t mxPart = 0;
-  for (const HLayer& L : M->L)
+  for (const HLayer& L : M->L) {
     if (L.sp.mixer == DSK_MIX_LATENT_SWA) mxPart = std::max(mxPart, (size_t)kAttnSplitTokens * L.sp.att_heads * kAttnSplitMax * (L.sp.att_kv_rank + 2));
+    if (L.sp.mixer == DSK_MIX_GQA) mxPart = std::max(mxPart, (size_t)kAttnSplitTokens * L.sp.att_heads * kAttnSplitMax * (L.sp.att_vdim + 2));
+  }
   rc |= salloc(S, (void**)&S->part, mxPart * 4);
   if ((int)Tc >= kPrefillMin) {   // buffers of the matrix-product attention path, unless a window is too long for them
+    // latent attention up-projects keys and values of all heads (fp32, then packed in the matrix type); grouped-query
+    // attention packs its cached key / value heads in fp32 (kf / vf) and needs a second score array when it mixes heads
     size_t keys = 0, hd = 0, hv = 0, heads = 0;
+    bool latent = false;
     for (const HLayer& L : M->L) {
-      if (L.sp.mixer != DSK_MIX_LATENT_SWA) continue;
+      if (L.sp.mixer == DSK_MIX_SSD) continue;
+      const size_t kh = L.sp.mixer == DSK_MIX_GQA ? L.sp.att_kv_heads : L.sp.att_heads;
+      latent |= L.sp.mixer == DSK_MIX_LATENT_SWA;
       keys = std::max<size_t>(keys, (size_t)std::min<long long>((long long)L.sp.att_window - 1, (long long)c.max_seq_len) + std::min<size_t>(Tc, kPrefillQ));
-      hd = std::max<size_t>(hd, (size_t)L.sp.att_heads * L.sp.att_dim); hv = std::max<size_t>(hv, (size_t)L.sp.att_heads * L.sp.att_vdim);
+      hd = std::max<size_t>(hd, kh * L.sp.att_dim); hv = std::max<size_t>(hv, kh * L.sp.att_vdim);
       heads = std::max<size_t>(heads, L.sp.att_heads);
     }
-    const size_t bytes = keys * (hd + hv) * (4 + M->wsize) + heads * kPrefillQ * keys * 4;
+    const size_t bytes = keys * (hd + hv) * (4 + (latent ? M->wsize : 0)) + heads * kPrefillQ * keys * 4 * (any_talk ? 2 : 1);
     if (keys > 0 && bytes <= ((size_t)4 << 30)) {
       S->prefill_keys = (int)keys;
       rc |= salloc(S, (void**)&S->kf, keys * hd * 4) | salloc(S, (void**)&S->vf, keys * hv * 4);
-      rc |= salloc(S, &S->kb, keys * hd * M->wsize) | salloc(S, &S->vt, keys * hv * M->wsize);
+      if (latent) rc |= salloc(S, &S->kb, keys * hd * M->wsize) | salloc(S, &S->vt, keys * hv * M->wsize);
       rc |= salloc(S, (void**)&S->sc, heads * kPrefillQ * keys * 4) | salloc(S, (void**)&S->d_rows, keys * 4);
+      if (any_talk) rc |= salloc(S, (void**)&S->sc2, heads * kPrefillQ * keys * 4);
     }
   }
   rc |= salloc(S, (void**)&S->x, Tc * c.dim * 4) | salloc(S, (void**)&S->h, Tc * c.dim * 4);
+  if (c.block == DSK_BLOCK_SANDWICH) rc |= salloc(S, (void**)&S->y, Tc * c.dim * 4);
   rc |= salloc(S, (void**)&S->b0, Tc * mx0 * 4) | salloc(S, (void**)&S->b1, Tc * mx1 * 4) | salloc(S, (void**)&S->b2, Tc * mx2 * 4) | salloc(S, (void**)&S->b3, Tc * mx3 * 4);
   rc |= salloc(S, (void**)&S->wgt, Tc * mxTop * 4) | salloc(S, (void**)&S->d_idx, Tc * mxTop * 4) | salloc(S, (void**)&S->d_perm, Tc * mxTop * 4);
   rc |= salloc(S, (void**)&S->d_tiles, (size_t)S->max_tiles * sizeof(int4)) | salloc(S, (void**)&S->d_ntiles, 16);
@@ -510,7 +677,7 @@ static void timeline_report(State* S, int T) {
 static GemmP gp(const float* A, int lda, const void* W, int ldw, float* C, int ldc, int M, int N, int K) {
   GemmP P{};
   P.A = A; P.lda = lda; P.W = W; P.ldw = ldw; P.C = C; P.ldc = ldc; P.M = M; P.N = N; P.K = K;
-  P.a_div = 1; P.z_adiv = 1; P.alpha = 1.f;
+  P.a_div = 1; P.z_adiv = 1; P.z_wdiv = 1; P.alpha = 1.f;
   return P;
 }
 
@@ -521,6 +688,7 @@ static void launch_gemm_mma(int epi, const GemmP& P, int Z, int tile_cap, cudaSt
     case HEPI_STORE: gemm_mma<HEPI_STORE><<<grid, 256, kMmaSmem, st>>>(P); break;
     case HEPI_ADD: gemm_mma<HEPI_ADD><<<grid, 256, kMmaSmem, st>>>(P); break;
     case HEPI_GLU: gemm_mma<HEPI_GLU><<<grid, 256, kMmaSmem, st>>>(P); break;
+    case HEPI_XIELU: gemm_mma<HEPI_XIELU><<<grid, 256, kMmaSmem, st>>>(P); break;
     default: gemm_mma<HEPI_GELU_MUL><<<grid, 256, kMmaSmem, st>>>(P); break;
   }
 }
@@ -533,6 +701,7 @@ static void launch_gemm_t(int epi, const GemmP& P, int Z, bool small, int tile_c
       case HEPI_STORE: gemv_rows<WT, HEPI_STORE><<<grid, 256, 0, st>>>(P); break;
       case HEPI_ADD: gemv_rows<WT, HEPI_ADD><<<grid, 256, 0, st>>>(P); break;
       case HEPI_GLU: gemv_rows<WT, HEPI_GLU><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_XIELU: gemv_rows<WT, HEPI_XIELU><<<grid, 256, 0, st>>>(P); break;
       default: gemv_rows<WT, HEPI_GELU_MUL><<<grid, 256, 0, st>>>(P); break;
     }
   } else {
@@ -541,6 +710,7 @@ static void launch_gemm_t(int epi, const GemmP& P, int Z, bool small, int tile_c
       case HEPI_STORE: gemm_tiled<WT, HEPI_STORE><<<grid, 256, 0, st>>>(P); break;
       case HEPI_ADD: gemm_tiled<WT, HEPI_ADD><<<grid, 256, 0, st>>>(P); break;
       case HEPI_GLU: gemm_tiled<WT, HEPI_GLU><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_XIELU: gemm_tiled<WT, HEPI_XIELU><<<grid, 256, 0, st>>>(P); break;
       default: gemm_tiled<WT, HEPI_GELU_MUL><<<grid, 256, 0, st>>>(P); break;
     }
   }
@@ -583,7 +753,9 @@ static void launch_scan(const dsk_layer_spec& sp, const float* proj, int ld_proj
 #undef DSK_SCAN
 }
 
-static void launch_attn(const float* qa, const float* cache, float* out, int T, int H, int R, const int* ctl, int window, int ring,
+static int R0(const Model* M, size_t ri) { return M->runs[ri].owner_run; }
+
+static void launch_attn(const float* qa, const float* cache, float* out, int T, int H, int R, const int* ctl, int mask, int window, int ring,
                         float scale, float* part, cudaStream_t st) {
   const int TQ = T >= 8 ? 8 : T >= 4 ? 4 : T >= 2 ? 2 : 1, HB = 8 / TQ;
   int NS = 1;
@@ -593,10 +765,10 @@ static void launch_attn(const float* qa, const float* cache, float* out, int T, 
   }
   const dim3 grid((unsigned)((T + TQ - 1) / TQ), (unsigned)((H + HB - 1) / HB), (unsigned)NS);
   const size_t smem = ((size_t)8 * R + (size_t)32 * (R + 1)) * 4;
-  if (R <= 128) latent_swa_attn<float, 4><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ, NS, part);
-  else if (R <= 256) latent_swa_attn<float, 8><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ, NS, part);
-  else if (R <= 512) latent_swa_attn<float, 16><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ, NS, part);
-  else latent_swa_attn<float, 32><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, window, ring, scale, TQ, NS, part);
+  if (R <= 128) latent_swa_attn<float, 4><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, mask, window, ring, scale, TQ, NS, part);
+  else if (R <= 256) latent_swa_attn<float, 8><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, mask, window, ring, scale, TQ, NS, part);
+  else if (R <= 512) latent_swa_attn<float, 16><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, mask, window, ring, scale, TQ, NS, part);
+  else latent_swa_attn<float, 32><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, mask, window, ring, scale, TQ, NS, part);
   if (NS > 1) latent_swa_merge<<<T * H, 128, 0, st>>>(part, out, R, NS);
 }
 
@@ -605,14 +777,24 @@ static void enqueue_head(dsk_model* m, dsk_state* s, int first, int count, cudaS
   Model* M = m->hy;
   State* S = s->hy;
   const dsk_hybrid_config& c = M->c;
-  GemmP P = gp(S->h, c.dim, M->embed.p, c.dim, S->logits, c.vocab_size, count, c.vocab_size, c.dim);
+  GemmP P = gp(S->h, c.dim, c.tie_head ? M->embed.p : M->head.p, c.dim, S->logits, c.vocab_size, count, c.vocab_size, c.dim);
   P.a_map = S->d_want + first; P.alpha = c.logit_scale;
   linear(S, c.quant == DSK_BF16, HEPI_STORE, P, 1, st);
 }
 
+// the model's norm over the T rows of `in` (width values each): stored into `out`, or added into it times alpha (mode 1)
+static void norm_rows(const dsk_hybrid_config& c, State* S, const float* in, const float* w, float* out, int T, int mode, float alpha, cudaStream_t st) {
+  if (c.norm_kind == DSK_NORM_LAYER) layer_norm<<<T, 256, 0, st>>>(in, c.dim, w, out, c.dim, c.dim, c.norm_eps, mode, alpha);
+  else group_rmsnorm<float><<<T, 256, 0, st>>>(in, c.dim, w, out, c.dim, c.dim, c.norm_groups, c.norm_eps, mode, alpha, nullptr, 0);
+  S->launches++;
+}
+
+// where a sublayer's last product goes: added into the residual stream (parallel blocks), or stored for the closing norm
+struct Sink { int epi; float* C; float alpha; };
+
 // Enqueues the kernels of one chunk of T <= chunk tokens (ids in S->d_tok, first position in S->d_ctl) on `st`.
 // n_want > 0: the LM head runs on the rows listed in S->d_want -> S->logits [n_want][vocab].  trace (device, nullable):
-// [layers][T][width] copies of the residual stream after every layer.
+// [layer runs][T][width] copies of the residual stream after every layer run.
 // pos0 >= 0: the first position as the host knows it (portions may then take the matrix-product attention path); -1 inside a
 // captured step, where positions live in device memory only.
 static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* trace, cudaStream_t st, int pos0 = -1) {
@@ -620,6 +802,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
   State* S = s->hy;
   const dsk_hybrid_config& c = M->c;
   const bool bf = c.quant == DSK_BF16;
+  const bool sandwich = c.block == DSK_BLOCK_SANDWICH;
   const int W = c.dim;
   const float mult = c.residual_mult;
   if (bf) embed_rows<__nv_bfloat16><<<T, 256, 0, st>>>(S->d_tok, (const __nv_bfloat16*)M->embed.p, W, S->x);
@@ -629,13 +812,71 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
   const bool tl = S->timeline && pos0 >= 0;
   auto MK = [&](const char* label) { if (tl) mark(S, label, st); };
   MK("embed");
-  for (int li = 0; li < c.n_layers; li++) {
+  const Sink to_x{HEPI_ADD, S->x, mult}, to_y{HEPI_STORE, S->y, 1.f};
+  for (size_t ri = 0; ri < M->runs.size(); ri++) {
+    const Run& run = M->runs[ri];
+    const int li = run.layer;
     const HLayer& L = M->L[li];
     const dsk_layer_spec& sp = L.sp;
-    LayerState& ls = S->L[li];
-    group_rmsnorm<float><<<T, 256, 0, st>>>(S->x, W, L.norm1, S->h, W, W, c.norm_groups, c.norm_eps, 0, 0.f, nullptr, 0);
-    S->launches++;
-    if (is_ssd(sp)) {
+    LayerState& ls = S->L[ri];
+    if (run.pass >= 0) {   // a pass of the layer loop opens with its own vector added to the residual stream
+      add_row<<<T, 256, 0, st>>>(S->x, W, M->loop_step + (size_t)run.pass * W, W);
+      S->launches++;
+    }
+    norm_rows(c, S, S->x, L.norm1, S->h, T, 0, 0.f, st);
+    const Sink sink = sandwich ? to_y : to_x;
+    if (sp.mixer == DSK_MIX_GQA) {
+      const int H = sp.att_heads, G = sp.att_kv_heads, D = sp.att_dim, V = sp.att_vdim, HD = H * D, GD = G * D, GV = G * V, rep = H / G;
+      float *kc = (float*)ls.cache, *vc = (float*)ls.vcache;
+      MK("norm");
+      linear(S, bf, HEPI_STORE, gp(S->h, W, L.q.p, W, S->b0, HD, T, HD, W), 1, st);
+      linear(S, bf, HEPI_STORE, gp(S->h, W, L.kproj.p, W, S->b1, GD, T, GD, W), 1, st);
+      MK("att.qk");
+      qk_norm_rope<<<T, 256, 0, st>>>(S->b0, S->b2, HD, S->b1, nullptr, GD, GV, L.q_norm, L.k_norm, c.norm_eps, D, sp.rot_dims, L.rot_freq,
+                                      L.rot_mag, S->d_ctl, kc, vc, L.ring);
+      S->launches++;
+      MK("att.norm+rot");
+      if (pos0 >= 0 && T >= kPrefillMin && S->prefill_keys > 0) {
+        // a portion: blocks of kPrefillQ queries, each as  scores = q k^T per head (fp32);  mixing of the heads;  masked softmax;  o = P v
+        for (int t0 = 0; t0 < T; t0 += kPrefillQ) {
+          const int Tq = std::min(kPrefillQ, T - t0), qpos0 = pos0 + t0;
+          const int first = mask_first(sp.att_mask, sp.att_window, qpos0), Lk = qpos0 + Tq - first;
+          pack_ring_kv<float><<<Lk, 256, 0, st>>>(kc, vc, S->kf, S->vf, first, Lk, L.ring, G, D, V);
+          S->launches++;
+          MK("att.pack");
+          GemmP Sc = gp(S->b2 + (size_t)t0 * HD, HD, S->kf, D, S->sc, Lk, Tq, Lk, D);
+          Sc.sA = D; Sc.sW = (long long)Lk * D; Sc.z_wdiv = rep; Sc.sC = (long long)Tq * Lk; Sc.alpha = sp.att_scale;
+          linear(S, false, HEPI_STORE, Sc, H, st);
+          MK("att.scores");
+          float* pr = S->sc;
+          if (sp.att_talk) {
+            const long long n = (long long)Tq * Lk;
+            mix_heads<<<(unsigned)((n + 127) / 128), 128, (size_t)(H * H + H * 128) * 4, st>>>(S->sc, S->sc2, L.talk, H, n);
+            S->launches++;
+            pr = S->sc2;
+          }
+          softmax_band<<<dim3((unsigned)Tq, (unsigned)H), 128, 0, st>>>(pr, Tq, Lk, first, qpos0, sp.att_mask, sp.att_window);
+          S->launches++;
+          MK("att.softmax");
+          GemmP Ov = gp(pr, Lk, S->vf, Lk, S->b3 + (size_t)t0 * H * V, H * V, Tq, V, Lk);
+          Ov.sA = (long long)Tq * Lk; Ov.sW = (long long)V * Lk; Ov.z_wdiv = rep; Ov.sC = V;
+          linear(S, false, HEPI_STORE, Ov, H, st);
+          MK("att.pv");
+        }
+      } else {
+        int NS = 1;
+        if (T <= kAttnSplitTokens) NS = std::max(1, std::min((std::min(sp.att_window, L.ring) + 31) / 32, kAttnSplitMax));
+        gqa_attn<<<dim3((unsigned)T, (unsigned)NS), 256, gqa_attn_smem_floats(H, G, D, V) * 4, st>>>(
+            S->b2, kc, vc, S->b3, sp.att_talk ? L.talk : nullptr, T, H, G, D, V, S->d_ctl, sp.att_mask, sp.att_window, L.ring, sp.att_scale, NS, S->part);
+        if (NS > 1) latent_swa_merge<<<T * H, 128, 0, st>>>(S->part, S->b3, V, NS);
+        S->launches += NS > 1 ? 2 : 1;
+        MK("att.decode");
+      }
+      GemmP P = gp(S->b3, H * V, L.o.p, H * V, sink.C, W, T, W, H * V);
+      P.alpha = sink.alpha;
+      linear(S, bf, sink.epi, P, 1, st);
+      MK("att.o");
+    } else if (is_ssd(sp)) {
       const int inner = (int)ssd_inner(sp), ch = (int)ssd_channels(sp), pw = (int)ssd_proj(sp);
       MK("norm");
       linear(S, bf, HEPI_STORE, gp(S->h, W, L.in.p, W, S->b0, pw, T, pw, W), 1, st);
@@ -648,14 +889,14 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       group_rmsnorm<float><<<T, 256, 0, st>>>(S->b2, inner, L.mnorm, S->b3, inner, inner, sp.ssm_norm_groups, c.norm_eps, 0, 0.f, nullptr, 0);
       S->launches += 4;
       MK("ssd.norm");
-      GemmP P = gp(S->b3, inner, L.o.p, inner, S->x, W, T, W, inner);
-      P.alpha = mult;
-      linear(S, bf, HEPI_ADD, P, 1, st);
+      GemmP P = gp(S->b3, inner, L.o.p, inner, sink.C, W, T, W, inner);
+      P.alpha = sink.alpha;
+      linear(S, bf, sink.epi, P, 1, st);
       MK("ssd.o");
     } else {
       const int H = sp.att_heads, D = sp.att_dim, V = sp.att_vdim, R = sp.att_kv_rank;
       const HLayer& O = M->L[L.owner];
-      float* cache = (float*)S->L[L.owner].cache;
+      float* cache = (float*)S->L[R0(M, ri)].cache;
       MK("norm");
       linear(S, bf, HEPI_STORE, gp(S->h, W, L.q.p, W, S->b0, H * D, T, H * D, W), 1, st);
       if (L.owner == li) {
@@ -670,7 +911,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         ov = S->b3;
         for (int t0 = 0; t0 < T; t0 += kPrefillQ) {
           const int Tq = std::min(kPrefillQ, T - t0), qpos0 = pos0 + t0;
-          const int first = std::max(0, qpos0 - sp.att_window + 1), Lk = qpos0 + Tq - first;
+          const int first = mask_first(sp.att_mask, sp.att_window, qpos0), Lk = qpos0 + Tq - first;
           ring_rows<<<(Lk + 255) / 256, 256, 0, st>>>(first, Lk, O.ring, S->d_rows);
           GemmP K = gp(cache, R, L.uk.p, R, S->kf, H * D, Lk, H * D, R);
           K.a_map = S->d_rows;
@@ -686,7 +927,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
           MK("att.pack");
           linear(S, bf, HEPI_STORE, Sc, H, st);
           MK("att.scores");
-          softmax_band<<<dim3((unsigned)Tq, (unsigned)H), 128, 0, st>>>(S->sc, Tq, Lk, first, qpos0, sp.att_window);
+          softmax_band<<<dim3((unsigned)Tq, (unsigned)H), 128, 0, st>>>(S->sc, Tq, Lk, first, qpos0, sp.att_mask, sp.att_window);
           GemmP Ov = gp(S->sc, Lk, S->vt, Lk, S->b3 + (size_t)t0 * H * V, H * V, Tq, V, Lk);
           Ov.sA = (long long)Tq * Lk; Ov.sW = (long long)V * Lk; Ov.sC = V;
           MK("att.softmax");
@@ -700,7 +941,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
           P.sA = D; P.sW = (long long)R * D; P.sC = R;
           linear(S, bf, HEPI_STORE, P, H, st);
         }
-        launch_attn(S->b2, cache, S->b3, T, H, R, S->d_ctl, sp.att_window, O.ring, sp.att_scale, S->part, st);
+        launch_attn(S->b2, cache, S->b3, T, H, R, S->d_ctl, sp.att_mask, sp.att_window, O.ring, sp.att_scale, S->part, st);
         S->launches++;
         {  // value up-projection per head: ov[t][h][:] = W_uv[h] o[t][h][:]
           GemmP P = gp(S->b3, H * R, L.uv.p, R, S->b0, H * V, T, V, R);
@@ -709,10 +950,26 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         }
       }
       MK("att.absorbed");
-      GemmP P = gp(ov, H * V, L.o.p, H * V, S->x, W, T, W, H * V);
-      P.alpha = mult;
-      linear(S, bf, HEPI_ADD, P, 1, st);
+      GemmP P = gp(ov, H * V, L.o.p, H * V, sink.C, W, T, W, H * V);
+      P.alpha = sink.alpha;
+      linear(S, bf, sink.epi, P, 1, st);
       MK("att.o");
+    }
+    if (sandwich) {   // x += norm1b(mixer output); the feed-forward then reads norm2 of the new x
+      norm_rows(c, S, S->y, L.norm1b, S->x, T, 1, mult, st);
+      if (sp.ff_kind != DSK_FF_NONE) norm_rows(c, S, S->x, L.norm2, S->h, T, 0, 0.f, st);
+      MK("norm");
+    }
+    if (sp.ff_kind == DSK_FF_DENSE) {
+      const int ff = sp.ff_hidden;
+      GemmP U = gp(S->h, W, L.up.p, W, S->b2, ff, T, ff, W);
+      U.bias = L.up_b; U.act_a = L.act_a; U.act_b = L.act_b;
+      linear(S, bf, HEPI_XIELU, U, 1, st);
+      MK("ff.up");
+      GemmP Dn = gp(S->b2, ff, L.down.p, ff, sink.C, W, T, W, ff);
+      Dn.bias = L.down_b; Dn.alpha = sink.alpha;
+      linear(S, bf, sink.epi, Dn, 1, st);
+      MK("ff.down");
     }
     if (sp.ff_kind == DSK_FF_MOE) {
       const int E = sp.ff_experts, top = sp.ff_top, ff = sp.ff_hidden, pairs = T * top;
@@ -743,9 +1000,13 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         linear(S, bf, HEPI_STORE, Dn, 1, st, cap);
         MK("moe.down");
       }
-      moe_combine<<<T, 256, 0, st>>>(S->x, W, S->b3, S->wgt, top, W, mult);
+      moe_combine<<<T, 256, 0, st>>>(sink.C, W, S->b3, S->wgt, top, W, sink.alpha, sink.epi == HEPI_ADD ? 1 : 0);
       S->launches++;
       MK("moe.combine");
+    }
+    if (sandwich && sp.ff_kind != DSK_FF_NONE) {
+      norm_rows(c, S, S->y, L.norm2b, S->x, T, 1, mult, st);
+      MK("norm");
     }
     if (c.side_dim > 0) {
       const int sd = c.side_dim;
@@ -757,11 +1018,10 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       S->launches++;
       MK("side");
     }
-    if (trace) CKL(cudaMemcpyAsync(trace + (size_t)li * T * W, S->x, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st));
+    if (trace) CKL(cudaMemcpyAsync(trace + ri * (size_t)T * W, S->x, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st));
   }
   if (n_want > 0) {   // final norm of every row, LM head on the first group of wanted rows (enqueue_head does the others)
-    group_rmsnorm<float><<<T, 256, 0, st>>>(S->x, W, M->final_norm, S->h, W, W, c.norm_groups, c.norm_eps, 0, 0.f, nullptr, 0);
-    S->launches++;
+    norm_rows(c, S, S->x, M->final_norm, S->h, T, 0, 0.f, st);
     enqueue_head(m, s, 0, std::min(n_want, S->head_rows), st);
     MK("head");
   }
@@ -782,8 +1042,8 @@ static int forward_chunk(dsk_model* m, dsk_state* s, const int32_t* tokens, int 
   for (int i = 0; i < n; i++) if (tokens[i] < 0 || tokens[i] >= c.vocab_size) return fail(-4, "token %d out of range", tokens[i]);
   for (int i = 0; i < n_want; i++) if (want[i] < 0 || want[i] >= n || (i && want[i] <= want[i - 1])) return fail(-4, "wanted rows must be ascending indices into the chunk");
   for (const HLayer& L : M->L)   // a ring cache shortened to max_seq_len holds no position beyond it
-    if (L.sp.mixer == DSK_MIX_LATENT_SWA && M->L[L.owner].ring < L.sp.att_window - 1 + S->chunk && pos0 + n > M->L[L.owner].ring)
-      return fail(-4, "position %d does not fit the latent cache (max_seq_len %d)", pos0 + n - 1, c.max_seq_len);
+    if (L.owner >= 0 && M->L[L.owner].ring < L.sp.att_window - 1 + S->chunk && pos0 + n > M->L[L.owner].ring)
+      return fail(-4, "position %d does not fit the attention cache (max_seq_len %d)", pos0 + n - 1, c.max_seq_len);
   float* d_trace = nullptr;
   int wi = 0;
   for (int o = 0; o < n; o += S->chunk) {
@@ -795,7 +1055,7 @@ static int forward_chunk(dsk_model* m, dsk_state* s, const int32_t* tokens, int 
     CK(cudaMemcpyAsync(S->d_tok, S->h_tok, (size_t)T * 4, cudaMemcpyHostToDevice, s->stream));
     if (nw) CK(cudaMemcpyAsync(S->d_want, S->h_want, (size_t)nw * 4, cudaMemcpyHostToDevice, s->stream));
     set_ctl<<<1, 1, 0, s->stream>>>(S->d_ctl, pos0 + o);
-    if (host_layers) { CK(cudaMalloc((void**)&d_trace, (size_t)c.n_layers * T * c.dim * 4)); }
+    if (host_layers) { CK(cudaMalloc((void**)&d_trace, M->runs.size() * (size_t)T * c.dim * 4)); }
     if (enqueue_chunk(m, s, T, nw, d_trace, s->stream, pos0 + o)) { if (d_trace) cudaFree(d_trace); return -2; }
     for (int g0 = 0; g0 < nw; g0 += S->head_rows) {   // the LM head in groups of head_rows wanted rows
       const int gn = std::min(S->head_rows, nw - g0);
@@ -809,7 +1069,7 @@ static int forward_chunk(dsk_model* m, dsk_state* s, const int32_t* tokens, int 
     timeline_report(S, T);
     if (host_layers) {
       CK(cudaStreamSynchronize(s->stream));
-      for (int l = 0; l < c.n_layers; l++)
+      for (size_t l = 0; l < M->runs.size(); l++)
         CK(cudaMemcpy(host_layers + ((size_t)l * n + o) * c.dim, d_trace + (size_t)l * T * c.dim, (size_t)T * c.dim * 4, cudaMemcpyDeviceToHost));
       cudaFree(d_trace); d_trace = nullptr;
     }

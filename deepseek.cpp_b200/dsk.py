@@ -23,8 +23,12 @@ sys.path.insert(0, HERE)
 import dseek  # noqa: E402
 
 QUANT_IDS = {"fp32": 0, "fp16": 1, "f8e5m2": 2, "q2_k": 3, "q3_k": 4, "bf16": 5}
-MIX_SSD, MIX_LATENT_SWA = 0, 1
-FF_NONE, FF_MOE = 0, 1
+MIX_SSD, MIX_LATENT_SWA, MIX_GQA = 0, 1, 2
+FF_NONE, FF_MOE, FF_DENSE = 0, 1, 2
+MASK_WINDOW, MASK_CHUNK = 0, 1
+ACT_XIELU = 0
+BLOCK_PARALLEL, BLOCK_SANDWICH = 0, 1
+NORM_RMS, NORM_LAYER = 0, 1
 HYDRATE_KV_CACHE, OUTPUT_LOGITS = 0, 1
 
 f32p = C.POINTER(C.c_float)
@@ -88,18 +92,21 @@ class LayerSpec(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("mixer", "ssm_heads", "ssm_vdim", "ssm_state", "ssm_groups", "ssm_conv", "ssm_norm_groups",
                                        "att_heads", "att_dim", "att_vdim", "att_kv_rank", "att_window", "att_kv_from")] + \
                [("att_scale", C.c_float)] + [(n, C.c_int) for n in ("ff_kind", "ff_experts", "ff_top", "ff_hidden")] + \
-               [("ff_limit", C.c_float), ("ff_router_scale", C.c_float)]
+               [("ff_limit", C.c_float), ("ff_router_scale", C.c_float)] + \
+               [(n, C.c_int) for n in ("att_mask", "att_kv_heads", "att_talk", "rot_dims", "rot_original")] + \
+               [(n, C.c_float) for n in ("rot_base", "rot_factor", "rot_fast", "rot_slow")] + [("ff_act", C.c_int)]
 
 
 class HybridConfig(C.Structure):
     """dsk_hybrid_config (include/dsk.h)."""
     _fields_ = [(n, C.c_int) for n in ("dim", "vocab_size", "n_layers", "max_seq_len", "quant", "chunk")] + \
                [("norm_eps", C.c_float), ("norm_groups", C.c_int), ("residual_mult", C.c_float), ("logit_scale", C.c_float),
-                ("side_dim", C.c_int)]
+                ("side_dim", C.c_int)] + \
+               [(n, C.c_int) for n in ("block", "norm_kind", "tie_head", "loop_start", "loop_stop", "loop_times")]
 
 
 # mixer "type" strings of a layer-list config.json -> mixer kernel family.  Two names may map to one mechanism.
-MIXER_TYPES = {"mamba2": MIX_SSD, "mamba2_2": MIX_SSD, "latent_attention": MIX_LATENT_SWA}
+MIXER_TYPES = {"mamba2": MIX_SSD, "mamba2_2": MIX_SSD, "latent_attention": MIX_LATENT_SWA, "attention": MIX_GQA}
 
 
 def hybrid_from_config(cfg: dict, quant: str = "bf16", max_seq_len: int = 0, chunk: int = 256):
@@ -114,6 +121,7 @@ def hybrid_from_config(cfg: dict, quant: str = "bf16", max_seq_len: int = 0, chu
     hc.norm_eps, hc.norm_groups = float(norm.get("eps", 1e-5)), int(norm.get("groups", 1))
     hc.residual_mult, hc.logit_scale = float(cfg.get("residual_mult", 1.0)), float(cfg.get("logit_scale", 1.0))
     hc.side_dim = int((cfg.get("token_side") or {}).get("dim", 0))
+    hc.block, hc.norm_kind, hc.tie_head = BLOCK_PARALLEL, NORM_RMS, 1
     specs = (LayerSpec * len(layers))()
     for i, lc in enumerate(layers):
         sp, mx = specs[i], lc["mixer"]
@@ -144,11 +152,65 @@ def hybrid_from_config(cfg: dict, quant: str = "bf16", max_seq_len: int = 0, chu
     return hc, specs
 
 
+def _attention_spec(sp, mx: dict, i: int):
+    """Grouped-query attention mixer of a layer: sizes, score scale, mask, rotation (with optional YaRN scaling)."""
+    sp.mixer, sp.att_kv_from = MIX_GQA, -1
+    sp.att_heads, sp.att_kv_heads = int(mx["heads"]), int(mx.get("kv_heads", mx["heads"]))
+    sp.att_dim, sp.att_vdim, sp.att_scale = int(mx["dim"]), int(mx["vdim"]), float(mx["scale"])
+    mask = mx.get("mask") or {}
+    sp.att_mask = MASK_CHUNK
+    sp.att_window = int(mask["size"]) if "size" in mask else 1 << 30      # no mask size: one chunk, plain causal attention
+    sp.att_talk = 1
+    rot = mx.get("rot") or {}
+    sp.rot_dims, sp.rot_base = int(rot.get("dims", 0)), float(rot.get("base", 10000.0))
+    sc = rot.get("scaling")
+    if sc:
+        sp.rot_factor, sp.rot_original = float(sc["factor"]), int(sc["original"])
+        sp.rot_fast, sp.rot_slow = float(sc["fast"]), float(sc["slow"])
+        if not sp.rot_factor > 0:
+            raise DskError(f"layer {i}: rotation scaling factor must be positive")
+    else:
+        sp.rot_factor = 0.0
+
+
+def rutulix_from_config(cfg: dict, quant: str = "bf16", max_seq_len: int = 0, chunk: int = 256):
+    """config.json of the Rutulix design -> (HybridConfig, LayerSpec array): sandwich blocks with layer norms, grouped-query
+    attention whose values are the key projection (whole-projection query / key norm, partial interleaved rotation with YaRN
+    scaling, head mixing of the scores, chunk mask), dense xIELU feed-forwards with biases, an untied head and a layer loop."""
+    hc = HybridConfig()
+    layers = cfg["layers"]
+    hc.dim, hc.vocab_size, hc.n_layers = int(cfg["width"]), int(cfg["vocab"]), len(layers)
+    hc.quant, hc.chunk = QUANT_IDS[quant], int(chunk)
+    hc.max_seq_len = int(max_seq_len) if max_seq_len else 1 << 30
+    hc.norm_eps, hc.norm_groups = float(cfg["norm"]["eps"]), 1
+    hc.residual_mult, hc.logit_scale, hc.side_dim = 1.0, 1.0, 0
+    hc.block, hc.norm_kind, hc.tie_head = BLOCK_SANDWICH, NORM_LAYER, 0
+    loop = cfg.get("loop") or {}
+    hc.loop_start, hc.loop_stop, hc.loop_times = int(loop.get("start", 0)), int(loop.get("stop", 0)), int(loop.get("times", 1))
+    if hc.loop_times <= 1 or hc.loop_stop <= hc.loop_start:
+        hc.loop_start = hc.loop_stop = 0
+        hc.loop_times = 1
+    specs = (LayerSpec * len(layers))()
+    for i, lc in enumerate(layers):
+        sp = specs[i]
+        if lc["type"] != "attention":
+            raise DskError(f"layer {i}: unknown mixer type {lc['type']!r}")
+        _attention_spec(sp, lc["mixer"], i)
+        ff = lc.get("mlp")
+        if ff:
+            if ff.get("kind") != "dense":
+                raise DskError(f"layer {i}: unknown feed-forward kind {ff.get('kind')!r}")
+            sp.ff_kind, sp.ff_hidden, sp.ff_act = FF_DENSE, int(ff["ff"]), ACT_XIELU
+        else:
+            sp.ff_kind = FF_NONE
+    return hc, specs
+
+
 # config.json "architecture" -> builder of the C-ABI model description (the DeepSeek families come as .dseek metadata instead)
-ARCHITECTURES = {"Desarax": hybrid_from_config}
+ARCHITECTURES = {"Desarax": hybrid_from_config, "Rutulix": rutulix_from_config}
 
 _lib = None
-ABI_VERSION = 4   # DSK_ABI_VERSION (include/dsk.h)
+ABI_VERSION = 5   # DSK_ABI_VERSION (include/dsk.h)
 
 
 def build(force: bool = False) -> str:
@@ -176,6 +238,7 @@ def lib():
         L.dsk_last_error.restype = C.c_char_p
         L.dsk_model_create.restype = C.c_void_p
         L.dsk_model_create.argtypes = [C.POINTER(Config), C.c_int, C.c_int]
+        L.dsk_model_layer_runs.argtypes = [C.c_void_p]
         L.dsk_model_create_hybrid.restype = C.c_void_p
         L.dsk_model_create_hybrid.argtypes = [C.POINTER(HybridConfig), C.POINTER(LayerSpec), C.c_int, C.c_int]
         L.dsk_forward_chunk.argtypes = [C.c_void_p, C.c_void_p, i32p, C.c_int, C.c_int, i32p, C.c_int, f32p, f32p]
@@ -343,11 +406,11 @@ class Model:
 
     def forward_chunk(self, tokens, pos0: int, want=(), layers: bool = False, state=None):
         """A portion of consecutive tokens starting at position pos0 (dsk_forward_chunk).  Returns the logits of the `want`
-        rows [len(want), vocab] (and, with layers=True, the residual stream after every layer [layers, n, dim])."""
+        rows [len(want), vocab] (and, with layers=True, the residual stream after every layer run [layer runs, n, dim])."""
         tok = np.ascontiguousarray(tokens, dtype=np.int32)
         w = np.ascontiguousarray(list(want), dtype=np.int32)
         out = np.zeros((len(w), self.cfg.vocab_size), dtype=np.float32)
-        tr = np.zeros((self.cfg.n_layers, len(tok), self.cfg.dim), dtype=np.float32) if layers else None
+        tr = np.zeros((self.L.dsk_model_layer_runs(self.h), len(tok), self.cfg.dim), dtype=np.float32) if layers else None
         _ck(self.L.dsk_forward_chunk(self.h, state or self.s, tok.ctypes.data_as(i32p), len(tok), pos0,
                                      w.ctypes.data_as(i32p) if len(w) else None, len(w),
                                      _fp(out) if len(w) else None, _fp(tr) if layers else None))

@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define DSK_ABI_VERSION 4
+#define DSK_ABI_VERSION 5
 
 /* Quant: src/codec.h:79-85 (same numbering) */
 enum { DSK_F32 = 0, DSK_F16 = 1, DSK_F8E5M2 = 2, DSK_Q2_K = 3, DSK_Q3_K = 4,
@@ -64,9 +64,27 @@ typedef struct dsk_config {
  *                       values are per-head up-projections of the normalised latent; att_kv_from >= 0 reads another layer's
  *                       latent cache instead of projecting its own.
  * Every layer: h = norm(x) (RMS norm in norm_groups parts); x += residual_mult * (mixer(h) + ff(h)); then, with side_dim > 0,
- * a per-layer token embedding gated by gelu_tanh(side.gate x) is projected, RMS-normed and added (x += residual_mult * ...). */
-enum { DSK_MIX_SSD = 0, DSK_MIX_LATENT_SWA = 1 };
-enum { DSK_FF_NONE = 0, DSK_FF_MOE = 1 };
+ * a per-layer token embedding gated by gelu_tanh(side.gate x) is projected, RMS-normed and added (x += residual_mult * ...).
+ * (That is DSK_BLOCK_PARALLEL with DSK_NORM_RMS, the Desarax design; the Rutulix design is DSK_BLOCK_SANDWICH with
+ * DSK_NORM_LAYER, DSK_MIX_GQA mixers, DSK_FF_DENSE feed-forwards, an untied head and a layer loop.) */
+enum { DSK_MIX_SSD = 0, DSK_MIX_LATENT_SWA = 1, DSK_MIX_GQA = 2 };
+enum { DSK_FF_NONE = 0, DSK_FF_MOE = 1, DSK_FF_DENSE = 2 };
+enum { DSK_MASK_WINDOW = 0,   /* position i sees j with 0 <= i - j < att_window */
+       DSK_MASK_CHUNK = 1 };  /* position i sees j <= i with floor(i / att_window) == floor(j / att_window), counted from position 0 */
+enum { DSK_ACT_XIELU = 0 };   /* z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z/2;  (p, q) = tensor mlp.act */
+enum { DSK_BLOCK_PARALLEL = 0,   /* h = norm1(x); x += residual_mult (mixer(h) + ff(h)) */
+       DSK_BLOCK_SANDWICH = 1 }; /* x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))) */
+enum { DSK_NORM_RMS = 0,         /* x / sqrt(mean(x^2) + eps) * w in norm_groups parts */
+       DSK_NORM_LAYER = 1 };     /* (x - mean) / sqrt(mean((x - mean)^2) + eps) * w, no bias */
+/*   DSK_MIX_GQA         softmax attention with att_heads query heads over att_kv_heads cached key heads (query head h reads key head
+ *                       h / (att_heads / att_kv_heads)); the values are the key projection itself, as projected (no value matrix:
+ *                       att_vdim == att_dim); RMS norm with a weight over the whole query projection and over the whole key
+ *                       projection; rotary positions on the first rot_dims dimensions of every head, dimension 2i paired with 2i + 1,
+ *                       frequencies base^(-2i/rot_dims) with YaRN scaling when rot_factor > 0 (ramp between the dimensions where
+ *                       rot_original / wavelength = rot_fast and rot_slow; cos and sin times 0.1 ln(rot_factor) + 1); scores times
+ *                       att_scale; with att_talk the heads' scores are mixed before the softmax (score_h <- sum_g T[h][g] score_g,
+ *                       tensor mix.talk); mask att_mask of size att_window.  Carries a ring of keys and values per layer run.
+ *   DSK_FF_DENSE        down(act(up h + b_up)) + b_down with activation ff_act. */
 typedef struct dsk_layer_spec {
   int mixer;                                                            /* DSK_MIX_* */
   int ssm_heads, ssm_vdim, ssm_state, ssm_groups, ssm_conv, ssm_norm_groups;   /* DSK_MIX_SSD */
@@ -74,6 +92,11 @@ typedef struct dsk_layer_spec {
   float att_scale;
   int ff_kind, ff_experts, ff_top, ff_hidden;                           /* DSK_FF_MOE: sigmoid router with selection bias, */
   float ff_limit, ff_router_scale;                                      /* clamped GLU experts g*sigmoid(1.702 g)*(u + 1)   */
+  int att_mask;                                                         /* DSK_MASK_* of both attention mixers */
+  int att_kv_heads, att_talk;                                           /* DSK_MIX_GQA (with att_heads, att_dim, att_vdim, att_scale, att_window) */
+  int rot_dims, rot_original;                                           /* rot_dims 0: no rotation */
+  float rot_base, rot_factor, rot_fast, rot_slow;                       /* rot_factor <= 0: plain frequencies */
+  int ff_act;                                                           /* DSK_FF_DENSE: DSK_ACT_*, hidden size ff_hidden */
 } dsk_layer_spec;
 typedef struct dsk_hybrid_config {
   int dim, vocab_size, n_layers;
@@ -84,6 +107,12 @@ typedef struct dsk_hybrid_config {
   int norm_groups;
   float residual_mult, logit_scale;
   int side_dim;              /* per-layer token input width, 0 = none */
+  int block;                 /* DSK_BLOCK_*: how a layer combines its sublayers */
+  int norm_kind;             /* DSK_NORM_* of every norm outside the mixers */
+  int tie_head;              /* 1: the LM head is the embedding table; 0: tensor "head" */
+  int loop_start, loop_stop, loop_times;   /* layers loop_start .. loop_stop - 1 run loop_times times in a row with the same weights and a
+                                              cache / state of their own per pass; tensor loop.step [times][dim]: row t is added to the
+                                              residual stream right before pass t.  loop_times <= 1 or an empty range: every layer once */
 } dsk_hybrid_config;
 
 typedef struct dsk_model dsk_model;
@@ -150,12 +179,14 @@ int dsk_kv_write(dsk_model* m, int layer, int which, const uint16_t* src, size_t
 int dsk_forward(dsk_model* m, dsk_state* s, int token, int pos, int mode, float* host_logits, int* argmax);
 /* A portion of n_tokens consecutive tokens of the state's sequence, starting at position pos0 (prefill batching; n_tokens = 1
  * is a decode step).  want: ascending indices into `tokens` whose logits are copied to host_logits [n_want][vocab] (nullable);
- * host_layers (nullable, layer-list models only): [layers][n_tokens][dim] residual stream after every layer.  Layer-list
+ * host_layers (nullable, layer-list models only): [layer runs][n_tokens][dim] residual stream after every layer run.  Layer-list
  * models run the portion through their chunk kernels (cut into dsk_hybrid_config::chunk tokens at most) and continue from the
  * recurrent state and latent caches in `s`: pos0 must follow the previous call, pos0 == 0 starts a new sequence.  DeepSeek
  * models run one dsk_forward per token (their hydrate loop). */
 int dsk_forward_chunk(dsk_model* m, dsk_state* s, const int32_t* tokens, int n_tokens, int pos0, const int32_t* want, int n_want,
                       float* host_logits, float* host_layers);
+/* Layer runs of one forward pass: n_layers plus the repeats of the layer loop (the first size of host_layers above). */
+int dsk_model_layer_runs(const dsk_model* m);
 /* Gives back what the state's sequence holds (recurrent state, convolution history, latent caches); the next call starts at 0. */
 int dsk_state_reset(dsk_state* s);
 /* Model::_copy_embedding — src/infer.cpp:1217-1263. */
