@@ -907,7 +907,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope(const float* __restrict__ q,
     const float nrm = isq ? nq : nk;
     float v = src[c] * nrm * (w ? w[c] : 1.f);
     if (d < rot_dims) {
-      const int cp = c ^ 1;                                   // the other half of the pair (2i, 2i + 1)
+      const int cp = (d & 1) ? c - 1 : c + 1;                 // the other half of the pair (2i, 2i + 1), counted inside the head
       const float u = src[cp] * nrm * (w ? w[cp] : 1.f);
       const float a = fpos * freq[d >> 1];
       const float cs = cosf(a) * mag, sn = sinf(a) * mag;

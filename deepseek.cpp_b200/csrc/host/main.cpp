@@ -148,12 +148,13 @@ static bool hybrid_config_from(const JValue& j, const std::string& quant, int co
   hc->norm_eps = (float)j.at("norm").number("eps", 1e-5); hc->norm_groups = j.at("norm").integer("groups", 1);
   hc->residual_mult = (float)j.number("residual_mult", 1.0); hc->logit_scale = (float)j.number("logit_scale", 1.0);
   hc->side_dim = j.at("token_side").integer("dim", 0);
+  hc->block = DSK_BLOCK_PARALLEL; hc->norm_kind = DSK_NORM_RMS; hc->tie_head = 1;
   for (size_t i = 0; i < layers.arr.size(); i++) {
     const JValue& lc = layers.arr[i];
     const JValue& mx = lc.at("mixer");
     dsk_layer_spec sp{};
     sp.mixer = mixer_of(lc.at("type").str);
-    sp.att_kv_from = -1;
+    sp.att_kv_from = -1; sp.att_mask = DSK_MASK_WINDOW;
     if (sp.mixer == DSK_MIX_SSD) {
       sp.ssm_heads = mx.integer("heads", 0); sp.ssm_vdim = mx.integer("vdim", 0); sp.ssm_state = mx.integer("state", 0);
       sp.ssm_groups = mx.integer("groups", 1); sp.ssm_conv = mx.integer("conv", 0); sp.ssm_norm_groups = mx.integer("norm_groups", 1);
@@ -175,6 +176,52 @@ static bool hybrid_config_from(const JValue& j, const std::string& quant, int co
   return true;
 }
 
+// The Rutulix design: sandwich blocks with layer norms, grouped-query attention (values = key projection, whole-projection
+// query / key norm, partial rotation with YaRN scaling, head mixing, chunk mask), dense xIELU feed-forwards, untied head, layer loop.
+static bool rutulix_config_from(const JValue& j, const std::string& quant, int context, dsk_hybrid_config* hc, std::vector<dsk_layer_spec>* specs) {
+  const JValue& layers = j.at("layers");
+  if (layers.kind != JValue::Arr || layers.arr.empty()) { fprintf(stderr, "FATAL: config.json has no layers\n"); return false; }
+  *hc = dsk_hybrid_config{};
+  hc->dim = j.integer("width", 0); hc->vocab_size = j.integer("vocab", 0); hc->n_layers = (int)layers.arr.size();
+  hc->max_seq_len = context > 0 ? context : 1 << 30;
+  hc->quant = quant == "fp32" ? DSK_F32 : DSK_BF16;
+  hc->chunk = context > 0 ? std::min(256, context) : 256;
+  hc->norm_eps = (float)j.at("norm").number("eps", 1e-5); hc->norm_groups = 1;
+  hc->residual_mult = 1.f; hc->logit_scale = 1.f;
+  hc->block = DSK_BLOCK_SANDWICH; hc->norm_kind = DSK_NORM_LAYER; hc->tie_head = 0;
+  const JValue& loop = j.at("loop");
+  hc->loop_start = loop.integer("start", 0); hc->loop_stop = loop.integer("stop", 0); hc->loop_times = loop.integer("times", 1);
+  if (hc->loop_times <= 1 || hc->loop_stop <= hc->loop_start) { hc->loop_start = hc->loop_stop = 0; hc->loop_times = 1; }
+  for (size_t i = 0; i < layers.arr.size(); i++) {
+    const JValue& lc = layers.arr[i];
+    const JValue& mx = lc.at("mixer");
+    if (lc.at("type").str != "attention") { fprintf(stderr, "FATAL: layer %zu: unknown mixer type %s\n", i, lc.at("type").str.c_str()); return false; }
+    dsk_layer_spec sp{};
+    sp.mixer = DSK_MIX_GQA; sp.att_kv_from = -1;
+    sp.att_heads = mx.integer("heads", 0); sp.att_kv_heads = mx.integer("kv_heads", sp.att_heads);
+    sp.att_dim = mx.integer("dim", 0); sp.att_vdim = mx.integer("vdim", 0); sp.att_scale = (float)mx.number("scale", 1.0);
+    sp.att_mask = DSK_MASK_CHUNK; sp.att_window = mx.at("mask").integer("size", 1 << 30); sp.att_talk = 1;
+    const JValue& rot = mx.at("rot");
+    sp.rot_dims = rot.integer("dims", 0); sp.rot_base = (float)rot.number("base", 10000.0);
+    if (rot.has("scaling")) {
+      const JValue& sc = rot.at("scaling");
+      sp.rot_factor = (float)sc.number("factor", 0.0); sp.rot_original = sc.integer("original", 0);
+      sp.rot_fast = (float)sc.number("fast", 0.0); sp.rot_slow = (float)sc.number("slow", 0.0);
+      if (!(sp.rot_factor > 0.f)) { fprintf(stderr, "FATAL: layer %zu: rotation scaling factor must be positive\n", i); return false; }
+    }
+    if (lc.has("mlp")) {
+      const JValue& ff = lc.at("mlp");
+      if (ff.at("kind").str != "dense") { fprintf(stderr, "FATAL: layer %zu: unknown feed-forward kind %s\n", i, ff.at("kind").str.c_str()); return false; }
+      sp.ff_kind = DSK_FF_DENSE; sp.ff_hidden = ff.integer("ff", 0); sp.ff_act = DSK_ACT_XIELU;
+    }
+    specs->push_back(sp);
+  }
+  return true;
+}
+
+// config.json "architecture" -> builder of the C-ABI model description
+typedef bool (*ArchBuilder)(const JValue&, const std::string&, int, dsk_hybrid_config*, std::vector<dsk_layer_spec>*);
+static const struct { const char* name; ArchBuilder build; } kArchitectures[] = {{"Desarax", hybrid_config_from}, {"Rutulix", rutulix_config_from}};
 
 // completion over token ids: the prompt goes through dsk_forward_chunk (prefill in portions), then the usual
 // dsk_sample -> dsk_forward loop; the ids are printed (these checkpoints carry no tokenizer).
@@ -186,7 +233,9 @@ static int run_layer_list(const std::string& dir, const std::string& quant, cons
   JValue cfg; JReader jr{text.data(), text.data() + text.size(), ""};
   if (!jr.parse(cfg) || cfg.kind != JValue::Obj) { fprintf(stderr, "FATAL: config.json: %s\n", jr.err.c_str()); return 1; }
   const std::string arch = cfg.at("architecture").str;
-  if (arch != "Desarax") { fprintf(stderr, "FATAL: unknown architecture '%s' (known: Desarax)\n", arch.c_str()); return 1; }
+  ArchBuilder builder = nullptr;
+  for (const auto& a : kArchitectures) if (arch == a.name) builder = a.build;
+  if (!builder) { fprintf(stderr, "FATAL: unknown architecture '%s' (known: Desarax, Rutulix)\n", arch.c_str()); return 1; }
   if (quant != "bf16" && quant != "fp32") { fprintf(stderr, "FATAL: -q must be bf16 or fp32\n"); return 1; }
   std::vector<int> enc;
   for (size_t i = 0; i < prompt_ids.size();) {
@@ -196,7 +245,7 @@ static int run_layer_list(const std::string& dir, const std::string& quant, cons
   }
   if (enc.empty()) { fprintf(stderr, "No prompt provided (-I <ids>)\n"); return 1; }
   dsk_hybrid_config hc; std::vector<dsk_layer_spec> specs;
-  if (!hybrid_config_from(cfg, quant, context, &hc, &specs)) return 1;
+  if (!builder(cfg, quant, context, &hc, &specs)) return 1;
   DseekData data;
   std::string err = data.load_shard(dir + "/model.safetensors", lock);
   if (!err.empty()) { fprintf(stderr, "failed to load checkpoint: %s\n", err.c_str()); return 1; }

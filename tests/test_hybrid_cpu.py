@@ -78,3 +78,62 @@ def test_oracle_window_and_carry(ho):
     seq = ho.Sequence(cfg2, W2)
     rows = [seq.feed(int(t)) for t in np.arange(20) % 61]
     assert np.allclose(np.array(rows), full, rtol=0, atol=1e-12)
+
+
+# ---- the Rutulix design ---------------------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def ro():
+    import rutulix_oracle
+    return rutulix_oracle
+
+
+def test_rutulix_config_to_layer_specs(ro):
+    import dsk
+    cfg = ro.small_config()
+    hc, specs = dsk.ARCHITECTURES[cfg["architecture"]](cfg, quant="bf16", max_seq_len=77, chunk=16)
+    assert (hc.dim, hc.vocab_size, hc.n_layers, hc.max_seq_len, hc.chunk, hc.side_dim) == (44, 61, 4, 77, 16, 0)
+    assert (hc.block, hc.norm_kind, hc.tie_head) == (dsk.BLOCK_SANDWICH, dsk.NORM_LAYER, 0)
+    assert (hc.loop_start, hc.loop_stop, hc.loop_times) == (1, 3, 3) and hc.quant == dsk.QUANT_IDS["bf16"]
+    a, b, c = specs[0], specs[1], specs[2]
+    assert (a.mixer, a.att_heads, a.att_kv_heads, a.att_dim, a.att_vdim, a.att_mask, a.att_window, a.att_talk) == (dsk.MIX_GQA, 6, 2, 10, 10, dsk.MASK_CHUNK, 7, 1)
+    assert (a.rot_dims, a.rot_original) == (6, 64) and abs(a.rot_base - 500.0) < 1e-3 and (a.rot_factor, a.rot_fast, a.rot_slow) == (4.0, 8.0, 1.0)
+    assert (a.ff_kind, a.ff_hidden, a.ff_act) == (dsk.FF_DENSE, 28, dsk.ACT_XIELU) and abs(a.att_scale - 0.3) < 1e-7
+    assert b.ff_kind == dsk.FF_NONE and b.rot_factor == 0.0 and b.rot_dims == 12       # no scaling: plain frequencies
+    assert c.att_kv_heads == 1 and abs(c.rot_slow - 0.5) < 1e-7
+    cfg["loop"]["times"] = 1                                                           # one pass is no loop
+    assert dsk.rutulix_from_config(cfg)[0].loop_times == 1 and dsk.rutulix_from_config(cfg)[0].loop_stop == 0
+    cfg["layers"][1]["type"] = "latent_attention"
+    with pytest.raises(dsk.DskError):
+        dsk.rutulix_from_config(cfg)
+
+
+def test_rutulix_oracle_invariants(ro):
+    """(1) the chunk mask: with one attention layer a token of the chunk before cannot change the logits, a token of the own chunk
+    does; (2) the loop's run order; (3) a sequence fed in two parts equals the whole; (4) rotation keeps a pair's length up to
+    the magnitude factor and depends on the position difference only."""
+    cfg = ro.model_config([ro.att(heads=2, dim=4, size=4, dims=2, ff=8)], width=16, vocab=23)
+    W = ro.random_weights(cfg, 4)
+    toks = np.arange(12) % 23
+    base = ro.run(cfg, W, toks)[0][-1]                   # position 11 sees 8 .. 11
+    out, ins = toks.copy(), toks.copy()
+    out[7] += 1
+    ins[8] += 1
+    assert np.array_equal(ro.run(cfg, W, out)[0][-1], base)
+    assert np.abs(ro.run(cfg, W, ins)[0][-1] - base).max() > 1e-6
+    cfg2 = ro.small_config()
+    assert ro.layer_runs(cfg2) == [(0, None), (1, 0), (2, None), (1, 1), (2, None), (1, 2), (2, None), (3, None)]
+    W2 = ro.random_weights(cfg2, 5)
+    whole = ro.run(cfg2, W2, np.arange(20) % 61)[0]
+    seq = ro.Sequence(cfg2, W2)
+    rows = [seq.feed(int(t)) for t in np.arange(20) % 61]
+    assert np.allclose(np.array(rows), whole, rtol=0, atol=1e-12)
+    rot = {"dims": 4, "base": 50.0, "scaling": {"factor": 3.0, "original": 16, "fast": 4.0, "slow": 0.5}}
+    _, mag = ro.rotation_table(rot)
+    v = np.random.RandomState(0).randn(2 * 6)
+    r5, r9 = ro.rotate_heads(v, 2, 6, rot, 5), ro.rotate_heads(v, 2, 6, rot, 9)
+    assert np.allclose(np.hypot(r5[:, 0], r5[:, 1]), mag * np.hypot(v.reshape(2, 6)[:, 0], v.reshape(2, 6)[:, 1]))
+    assert np.array_equal(r5[:, 4:], v.reshape(2, 6)[:, 4:])                          # beyond dims: unchanged
+    w = np.random.RandomState(1).randn(2 * 6)
+    d1 = (ro.rotate_heads(v, 2, 6, rot, 5) * ro.rotate_heads(w, 2, 6, rot, 2)).sum()
+    d2 = (ro.rotate_heads(v, 2, 6, rot, 9) * ro.rotate_heads(w, 2, 6, rot, 6)).sum()
+    assert abs(d1 - d2) < 1e-9
