@@ -500,7 +500,8 @@ __global__ void __launch_bounds__(256) gemv_rows(const GemmP P) {
     const WT* w = W + (size_t)n * P.ldw;
     const WT* w2 = DUAL ? W2 + (size_t)n * P.ldw : nullptr;
     if (vec) {
-      for (int k = lane * V; k < P.K; k += 32 * V) {
+#pragma unroll 4
+      for (int k = lane * V; k < P.K; k += 32 * V) {   // unrolled: several 16-byte weight loads in flight per lane
         float wv[V], wv2[V];
         WVec<WT>::load(w + k, wv);
         if (DUAL) WVec<WT>::load(w2 + k, wv2);
@@ -784,16 +785,21 @@ __global__ void __launch_bounds__(256) latent_swa_attn(const float* __restrict__
 
 // merges the NS partial softmax results of one (token, head): out = sum_s e^(m_s - m) acc_s / sum_s e^(m_s - m) l_s
 __global__ void latent_swa_merge(const float* __restrict__ part, float* __restrict__ out, int R, int NS) {
+  __shared__ float wts[64], ms[64];   // NS <= 64 (kAttnSplitMax)
   const size_t th = blockIdx.x;
   const float* pp = part + th * NS * (R + 2);
+  if ((int)threadIdx.x < NS) ms[threadIdx.x] = pp[(size_t)threadIdx.x * (R + 2)];
+  __syncthreads();
   float m = -1e30f;
-  for (int s = 0; s < NS; s++) m = fmaxf(m, pp[(size_t)s * (R + 2)]);
+  for (int s = 0; s < NS; s++) m = fmaxf(m, ms[s]);
+  if ((int)threadIdx.x < NS) wts[threadIdx.x] = expf(ms[threadIdx.x] - m);
+  __syncthreads();
   float l = 0.f;
-  for (int s = 0; s < NS; s++) l += expf(pp[(size_t)s * (R + 2)] - m) * pp[(size_t)s * (R + 2) + 1];
+  for (int s = 0; s < NS; s++) l = fmaf(wts[s], pp[(size_t)s * (R + 2) + 1], l);
   const float inv = 1.f / l;
   for (int r = threadIdx.x; r < R; r += blockDim.x) {
     float a = 0.f;
-    for (int s = 0; s < NS; s++) a = fmaf(expf(pp[(size_t)s * (R + 2)] - m), pp[(size_t)s * (R + 2) + 2 + r], a);
+    for (int s = 0; s < NS; s++) a = fmaf(wts[s], pp[(size_t)s * (R + 2) + 2 + r], a);
     out[th * R + r] = a * inv;
   }
 }
@@ -849,21 +855,75 @@ __global__ void __launch_bounds__(128) softmax_band(float* __restrict__ S, int T
 // Layer norm with a weight and no bias: (x - mean) / sqrt(mean((x - mean)^2) + eps) * w per row of n values.
 // mode 0: out = result; mode 1: out += alpha * result (a normalised sublayer output added into the residual stream).
 // ---------------------------------------------------------------------------------------------------------------------
+// A thread keeps its share of the row in registers (rows of up to 256 * kLnRegs values; longer rows are read again).
+constexpr int kLnRegs = 16;
+__device__ __forceinline__ void ln_stats(const float (&v)[kLnRegs], const float* __restrict__ x, int n, float eps, float* red, float& mean, float& sc) {
+  const bool cached = n <= 256 * kLnRegs;
+  float s = 0.f;
+  if (cached) {
+#pragma unroll
+    for (int k = 0; k < kLnRegs; k++) s += v[k];        // entries past the row's end are 0
+  } else for (int i = threadIdx.x; i < n; i += 256) s += x[i];
+  mean = block_sum(s, red) / (float)n;
+  float ss = 0.f;
+  if (cached) {
+#pragma unroll
+    for (int k = 0; k < kLnRegs; k++) { const float d = (int)threadIdx.x + 256 * k < n ? v[k] - mean : 0.f; ss = fmaf(d, d, ss); }
+  } else for (int i = threadIdx.x; i < n; i += 256) { const float d = x[i] - mean; ss = fmaf(d, d, ss); }
+  sc = 1.f / sqrtf(block_sum(ss, red) / (float)n + eps);
+}
+
 __global__ void __launch_bounds__(256) layer_norm(const float* __restrict__ in, int ld_in, const float* __restrict__ w,
                                                   float* __restrict__ out, int ld_out, int n, float eps, int mode, float alpha) {
   __shared__ float red[33];
   const int t = blockIdx.x;
   const float* x = in + (size_t)t * ld_in;
   float* o = out + (size_t)t * ld_out;
-  float s = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) s += x[i];
-  const float mean = block_sum(s, red) / (float)n;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) { const float d = x[i] - mean; ss = fmaf(d, d, ss); }
-  const float sc = 1.f / sqrtf(block_sum(ss, red) / (float)n + eps);
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = (x[i] - mean) * sc * w[i];
-    o[i] = mode == 0 ? v : o[i] + alpha * v;
+  float v[kLnRegs];
+  const bool cached = n <= 256 * kLnRegs;
+#pragma unroll
+  for (int k = 0; k < kLnRegs; k++) { const int i = threadIdx.x + 256 * k; v[k] = cached && i < n ? x[i] : 0.f; }
+  float mean, sc;
+  ln_stats(v, x, n, eps, red, mean, sc);
+  if (cached) {
+#pragma unroll
+    for (int k = 0; k < kLnRegs; k++) {
+      const int i = threadIdx.x + 256 * k;
+      if (i < n) { const float r = (v[k] - mean) * sc * w[i]; o[i] = mode == 0 ? r : o[i] + alpha * r; }
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += 256) { const float r = (x[i] - mean) * sc * w[i]; o[i] = mode == 0 ? r : o[i] + alpha * r; }
+  }
+}
+
+// The end of one sublayer and the start of the next in one pass over the row (rows of up to 256 * kLnRegs values):
+//   x += alpha * ln(y) * wy  (+ row, the vector of a loop pass that opens next);   h = ln(x) * wh
+__global__ void __launch_bounds__(256) layer_norm_add_norm(const float* __restrict__ y, const float* __restrict__ wy, float* __restrict__ x,
+                                                           const float* __restrict__ row, const float* __restrict__ wh,
+                                                           float* __restrict__ h, int n, float eps, float alpha) {
+  __shared__ float red[33];
+  const size_t t = blockIdx.x;
+  const float* yr = y + t * n;
+  float* xr = x + t * n;
+  float v[kLnRegs];
+#pragma unroll
+  for (int k = 0; k < kLnRegs; k++) { const int i = threadIdx.x + 256 * k; v[k] = i < n ? yr[i] : 0.f; }
+  float mean, sc;
+  ln_stats(v, yr, n, eps, red, mean, sc);
+#pragma unroll
+  for (int k = 0; k < kLnRegs; k++) {
+    const int i = threadIdx.x + 256 * k;
+    if (i < n) {
+      const float r = xr[i] + alpha * ((v[k] - mean) * sc * wy[i]) + (row ? row[i] : 0.f);
+      xr[i] = r;
+      v[k] = r;
+    } else v[k] = 0.f;
+  }
+  ln_stats(v, xr, n, eps, red, mean, sc);
+#pragma unroll
+  for (int k = 0; k < kLnRegs; k++) {
+    const int i = threadIdx.x + 256 * k;
+    if (i < n) h[t * n + i] = (v[k] - mean) * sc * wh[i];
   }
 }
 
@@ -910,7 +970,9 @@ __global__ void __launch_bounds__(256) qk_norm_rope(const float* __restrict__ q,
       const int cp = (d & 1) ? c - 1 : c + 1;                 // the other half of the pair (2i, 2i + 1), counted inside the head
       const float u = src[cp] * nrm * (w ? w[cp] : 1.f);
       const float a = fpos * freq[d >> 1];
-      const float cs = cosf(a) * mag, sn = sinf(a) * mag;
+      float sn, cs;
+      sincosf(a, &sn, &cs);
+      cs *= mag; sn *= mag;
       v = (d & 1) ? fmaf(v, cs, u * sn) : fmaf(v, cs, -u * sn);
     }
     if (isq) q_out[(size_t)t * HD + c] = v;
@@ -995,14 +1057,31 @@ __global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, con
       const float l = ls[h] * corr + warp_sum(p);
       ps[w * 32 + lane] = p;
       __syncwarp();
+      // weighted values: lane owns columns lane, lane + 32, ... (four at a time); eight keys per batch, so 32 loads are in flight
+      // per lane.  Keys past the tile's end have weight 0 and a row inside the ring (initialised memory), so no branch is needed.
       const float* vb = vc + (size_t)(h / rep) * Dv;
-      for (int r = lane; r < Dv; r += 32) {
-        float a = accs[h * Dv + r] * corr;
-        for (int jj = 0; jj < 32; jj++) {
-          const float pj = ps[w * 32 + jj];
-          if (pj != 0.f) a = fmaf(pj, vb[(size_t)rowoff[jj] * GV + r], a);
+      const float* pw = ps + w * 32;
+      for (int r0 = 0; r0 < Dv; r0 += 128) {
+        float a[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) { const int r = r0 + lane + 32 * u; a[u] = r < Dv ? accs[h * Dv + r] * corr : 0.f; }
+        for (int jj = 0; jj < 32; jj += 8) {
+          float v[8][4];
+#pragma unroll
+          for (int e = 0; e < 8; e++) {
+            const float* vr = vb + (size_t)rowoff[jj + e] * GV + r0 + lane;
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[e][u] = r0 + lane + 32 * u < Dv ? vr[32 * u] : 0.f;
+          }
+#pragma unroll
+          for (int e = 0; e < 8; e++) {
+            const float pj = pw[jj + e];
+#pragma unroll
+            for (int u = 0; u < 4; u++) a[u] = fmaf(pj, v[e][u], a[u]);
+          }
         }
-        accs[h * Dv + r] = a;
+#pragma unroll
+        for (int u = 0; u < 4; u++) { const int r = r0 + lane + 32 * u; if (r < Dv) accs[h * Dv + r] = a[u]; }
       }
       __syncwarp();
       if (lane == 0) { ms[h] = m_new; ls[h] = l; }

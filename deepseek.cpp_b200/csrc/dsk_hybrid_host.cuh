@@ -124,7 +124,7 @@ static int validate(const dsk_hybrid_config& c, const dsk_layer_spec* L) {
   if (c.side_dim < 0) return fail(-1, "negative side_dim");
   if (c.block != DSK_BLOCK_PARALLEL && c.block != DSK_BLOCK_SANDWICH) return fail(-1, "unknown block kind %d", c.block);
   if (c.norm_kind != DSK_NORM_RMS && c.norm_kind != DSK_NORM_LAYER) return fail(-1, "unknown norm kind %d", c.norm_kind);
-  if (c.loop_times > 1 && (c.loop_start < 0 || c.loop_stop > c.n_layers || c.loop_start > c.loop_stop))
+  if (c.loop_times >= 1 && (c.loop_start < 0 || c.loop_stop > c.n_layers || c.loop_start > c.loop_stop))
     return fail(-1, "layer loop %d..%d outside the %d layers", c.loop_start, c.loop_stop, c.n_layers);
   for (int i = 0; i < c.n_layers; i++) {
     const dsk_layer_spec& s = L[i];
@@ -216,7 +216,7 @@ static dsk_model* model_create(const dsk_hybrid_config* cfg, const dsk_layer_spe
     O.ring = (int)std::max<long long>(O.ring, std::min<long long>(need, (long long)cfg->max_seq_len));
   }
   // the order of layer runs: layers before the loop, the loop's passes, the layers after it
-  const bool looped = cfg->loop_times > 1 && cfg->loop_stop > cfg->loop_start;
+  const bool looped = cfg->loop_times >= 1 && cfg->loop_stop > cfg->loop_start;   // one pass is a loop too: it has its pass vector
   const int ls = looped ? cfg->loop_start : 0, le = looped ? cfg->loop_stop : 0, lt = looped ? cfg->loop_times : 0;
   for (int i = 0; i < ls; i++) M->runs.push_back(Run{i, -1, -1});
   for (int t = 0; t < lt; t++)
@@ -319,7 +319,7 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
     return MAT(M->head, c.vocab_size, c.dim);
   }
   if (nm == "loop.step") {
-    if (c.loop_times <= 1) return fail(-4, "tensor %s: the model has no layer loop", name);
+    if (c.loop_times < 1) return fail(-4, "tensor %s: the model has no layer loop", name);
     return F32(&M->loop_step, c.loop_times, c.dim);
   }
   if (nm == "side.embed") {
@@ -430,7 +430,7 @@ static int finalize(dsk_model* m) {
   if (!M->final_norm) return fail(-5, "missing tensor final.norm");
   if (c.side_dim > 0 && !M->side_embed.present) return fail(-5, "missing tensor side.embed");
   if (!c.tie_head && !M->head.present) return fail(-5, "missing tensor head");
-  if (c.loop_times > 1 && !M->loop_step) return fail(-5, "missing tensor loop.step");
+  if (c.loop_times >= 1 && c.loop_stop > c.loop_start && !M->loop_step) return fail(-5, "missing tensor loop.step");
   for (int i = 0; i < c.n_layers; i++) {
     HLayer& L = M->L[i];
     const dsk_layer_spec& s = L.sp;
@@ -490,14 +490,16 @@ static double active_bytes(const dsk_model* m) {
 }
 
 // kernels one decoded token launches (embedding + layers + final norm + LM head + arg-max)
+static bool fused_norms(const dsk_hybrid_config& c);
 static int launches_per_token(const dsk_model* m) {
   const Model* M = m->hy;
-  int n = 4;
+  int n = fused_norms(M->c) ? 3 : 4;
   const bool sandwich = M->c.block == DSK_BLOCK_SANDWICH;
   for (const Run& R : M->runs) {
     const HLayer& L = M->L[R.layer];
     const dsk_layer_spec& s = L.sp;
-    n += 1 + (R.pass >= 0 ? 1 : 0) + (sandwich ? 1 + (s.ff_kind != DSK_FF_NONE ? 2 : 0) : 0);
+    if (fused_norms(M->c)) n += 1 + (s.ff_kind != DSK_FF_NONE ? 1 : 0) + (&R == &M->runs[0] ? 1 + (R.pass >= 0 ? 1 : 0) : 0);
+    else n += 1 + (R.pass >= 0 ? 1 : 0) + (sandwich ? 1 + (s.ff_kind != DSK_FF_NONE ? 2 : 0) : 0);
     if (s.mixer == DSK_MIX_GQA) n += 6;   // q, k, norm + rotation, attention, merge, o
     else n += is_ssd(s) ? 5 + (s.ssm_conv > 1 ? 1 : 0) : 5 + (s.att_kv_from < 0 ? 2 : 0);
     if (s.ff_kind == DSK_FF_MOE) n += 5;
@@ -789,6 +791,10 @@ static void norm_rows(const dsk_hybrid_config& c, State* S, const float* in, con
   S->launches++;
 }
 
+static bool fused_norms(const dsk_hybrid_config& c) {
+  return c.block == DSK_BLOCK_SANDWICH && c.norm_kind == DSK_NORM_LAYER && c.dim <= 256 * kLnRegs && c.side_dim == 0;
+}
+
 // where a sublayer's last product goes: added into the residual stream (parallel blocks), or stored for the closing norm
 struct Sink { int epi; float* C; float alpha; };
 
@@ -813,17 +819,32 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
   auto MK = [&](const char* label) { if (tl) mark(S, label, st); };
   MK("embed");
   const Sink to_x{HEPI_ADD, S->x, mult}, to_y{HEPI_STORE, S->y, 1.f};
+  // sandwich blocks of layer norms: "x += ln(y); h = ln(x)" runs as one kernel (not while the residual stream is being recorded)
+  const bool fuse = fused_norms(c) && !trace;
+  bool h_ready = false;   // S->h already holds the norm that opens the coming run (or the final norm)
   for (size_t ri = 0; ri < M->runs.size(); ri++) {
     const Run& run = M->runs[ri];
     const int li = run.layer;
     const HLayer& L = M->L[li];
     const dsk_layer_spec& sp = L.sp;
     LayerState& ls = S->L[ri];
-    if (run.pass >= 0) {   // a pass of the layer loop opens with its own vector added to the residual stream
-      add_row<<<T, 256, 0, st>>>(S->x, W, M->loop_step + (size_t)run.pass * W, W);
-      S->launches++;
+    if (!h_ready) {
+      if (run.pass >= 0) {   // a pass of the layer loop opens with its own vector added to the residual stream
+        add_row<<<T, 256, 0, st>>>(S->x, W, M->loop_step + (size_t)run.pass * W, W);
+        S->launches++;
+      }
+      norm_rows(c, S, S->x, L.norm1, S->h, T, 0, 0.f, st);
     }
-    norm_rows(c, S, S->x, L.norm1, S->h, T, 0, 0.f, st);
+    h_ready = false;
+    // the closing norm of this run's last sublayer, fused with what opens the next run (its pass vector and first norm) or the head
+    auto close_run = [&](const float* wb) {
+      if (!fuse) { norm_rows(c, S, S->y, wb, S->x, T, 1, mult, st); return; }
+      const Run* next = ri + 1 < M->runs.size() ? &M->runs[ri + 1] : nullptr;
+      const float* row = next && next->pass >= 0 ? M->loop_step + (size_t)next->pass * W : nullptr;
+      layer_norm_add_norm<<<T, 256, 0, st>>>(S->y, wb, S->x, row, next ? M->L[next->layer].norm1 : M->final_norm, S->h, W, c.norm_eps, mult);
+      S->launches++;
+      h_ready = true;
+    };
     const Sink sink = sandwich ? to_y : to_x;
     if (sp.mixer == DSK_MIX_GQA) {
       const int H = sp.att_heads, G = sp.att_kv_heads, D = sp.att_dim, V = sp.att_vdim, HD = H * D, GD = G * D, GV = G * V, rep = H / G;
@@ -956,8 +977,14 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       MK("att.o");
     }
     if (sandwich) {   // x += norm1b(mixer output); the feed-forward then reads norm2 of the new x
-      norm_rows(c, S, S->y, L.norm1b, S->x, T, 1, mult, st);
-      if (sp.ff_kind != DSK_FF_NONE) norm_rows(c, S, S->x, L.norm2, S->h, T, 0, 0.f, st);
+      if (sp.ff_kind == DSK_FF_NONE) close_run(L.norm1b);
+      else if (fuse) {
+        layer_norm_add_norm<<<T, 256, 0, st>>>(S->y, L.norm1b, S->x, nullptr, L.norm2, S->h, W, c.norm_eps, mult);
+        S->launches++;
+      } else {
+        norm_rows(c, S, S->y, L.norm1b, S->x, T, 1, mult, st);
+        norm_rows(c, S, S->x, L.norm2, S->h, T, 0, 0.f, st);
+      }
       MK("norm");
     }
     if (sp.ff_kind == DSK_FF_DENSE) {
@@ -1005,7 +1032,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       MK("moe.combine");
     }
     if (sandwich && sp.ff_kind != DSK_FF_NONE) {
-      norm_rows(c, S, S->y, L.norm2b, S->x, T, 1, mult, st);
+      close_run(L.norm2b);
       MK("norm");
     }
     if (c.side_dim > 0) {
@@ -1021,7 +1048,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
     if (trace) CKL(cudaMemcpyAsync(trace + ri * (size_t)T * W, S->x, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st));
   }
   if (n_want > 0) {   // final norm of every row, LM head on the first group of wanted rows (enqueue_head does the others)
-    norm_rows(c, S, S->x, M->final_norm, S->h, T, 0, 0.f, st);
+    if (!h_ready) norm_rows(c, S, S->x, M->final_norm, S->h, T, 0, 0.f, st);
     enqueue_head(m, s, 0, std::min(n_want, S->head_rows), st);
     MK("head");
   }

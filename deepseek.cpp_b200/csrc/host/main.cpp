@@ -190,8 +190,7 @@ static bool rutulix_config_from(const JValue& j, const std::string& quant, int c
   hc->residual_mult = 1.f; hc->logit_scale = 1.f;
   hc->block = DSK_BLOCK_SANDWICH; hc->norm_kind = DSK_NORM_LAYER; hc->tie_head = 0;
   const JValue& loop = j.at("loop");
-  hc->loop_start = loop.integer("start", 0); hc->loop_stop = loop.integer("stop", 0); hc->loop_times = loop.integer("times", 1);
-  if (hc->loop_times <= 1 || hc->loop_stop <= hc->loop_start) { hc->loop_start = hc->loop_stop = 0; hc->loop_times = 1; }
+  if (j.has("loop")) { hc->loop_start = loop.integer("start", 0); hc->loop_stop = loop.integer("stop", 0); hc->loop_times = loop.integer("times", 0); }
   for (size_t i = 0; i < layers.arr.size(); i++) {
     const JValue& lc = layers.arr[i];
     const JValue& mx = lc.at("mixer");

@@ -185,11 +185,11 @@ def rutulix_from_config(cfg: dict, quant: str = "bf16", max_seq_len: int = 0, ch
     hc.norm_eps, hc.norm_groups = float(cfg["norm"]["eps"]), 1
     hc.residual_mult, hc.logit_scale, hc.side_dim = 1.0, 1.0, 0
     hc.block, hc.norm_kind, hc.tie_head = BLOCK_SANDWICH, NORM_LAYER, 0
-    loop = cfg.get("loop") or {}
-    hc.loop_start, hc.loop_stop, hc.loop_times = int(loop.get("start", 0)), int(loop.get("stop", 0)), int(loop.get("times", 1))
-    if hc.loop_times <= 1 or hc.loop_stop <= hc.loop_start:
-        hc.loop_start = hc.loop_stop = 0
-        hc.loop_times = 1
+    loop = cfg.get("loop")
+    if loop:            # a loop of one pass is still a loop: its pass vector is added before the range
+        hc.loop_start, hc.loop_stop, hc.loop_times = int(loop["start"]), int(loop["stop"]), int(loop["times"])
+    else:
+        hc.loop_start = hc.loop_stop = hc.loop_times = 0
     specs = (LayerSpec * len(layers))()
     for i, lc in enumerate(layers):
         sp = specs[i]

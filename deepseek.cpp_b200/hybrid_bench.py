@@ -1,5 +1,7 @@
-"""hybrid_bench.py — prefill and decode throughput of the layer-list family (Desarax design) at sizes that resemble a real
-model's layers, beside the closest DeepSeek model of the framework (true-MLA blocks, fp16) at equal width / depth / experts.
+"""hybrid_bench.py — prefill and decode throughput of the layer-list family at sizes that resemble a real model's layers.
+The Desarax sizes run beside the closest DeepSeek model of the framework (true-MLA blocks, fp16) at equal width / depth /
+experts; the Rutulix sizes run beside the closest layer-list model, a Desarax model of latent-attention layers at equal width,
+layer runs, heads, mask size and feed-forward matrix elements.
 
 Used by `bench.py --hybrid`.  Random weights generated on the GPU (bf16), uploaded through dsk_upload_tensor(src_on_device).
 Decode is the device-side greedy loop (CUDA events around the captured step graph); prefill is dsk_forward_chunk over a prompt
@@ -19,7 +21,82 @@ SIZES = {
                   att_vdim=64, kv_rank=256, window=512, experts=16, top=2, ff=512, side=32),
     "v2lite_like": dict(width=2048, vocab=102400, pattern="ssassAssassA", heads=64, vdim=64, state=128, groups=8, conv=4, att_heads=16,
                         att_dim=128, att_vdim=128, kv_rank=512, window=1024, experts=64, top=6, ff=1408, side=64),
+    # Rutulix: grouped-query attention layers with dense feed-forwards; layers loop[0] .. loop[1]-1 run loop[2] times
+    "rutulix_small": dict(design="Rutulix", width=1024, vocab=32000, n_layers=8, loop=(2, 4, 2), att_heads=16, kv_heads=4, att_dim=64, rot=32,
+                          window=512, ff=4096, kv_rank=256),
+    "rutulix_large": dict(design="Rutulix", width=2048, vocab=102400, n_layers=12, loop=(4, 8, 2), att_heads=16, kv_heads=4, att_dim=128, rot=64,
+                          window=1024, ff=8192, kv_rank=512),
 }
+
+
+def rutulix_config(z):
+    mx = {"heads": z["att_heads"], "kv_heads": z["kv_heads"], "dim": z["att_dim"], "vdim": z["att_dim"], "scale": z["att_dim"] ** -0.5,
+          "mask": {"size": z["window"]},
+          "rot": {"dims": z["rot"], "base": 10000.0, "scaling": {"factor": 8.0, "original": z["window"], "fast": 32.0, "slow": 1.0}}}
+    layers = [{"type": "attention", "mixer": dict(mx), "mlp": {"kind": "dense", "ff": z["ff"]}} for _ in range(z["n_layers"])]
+    return {"architecture": "Rutulix", "vocab": z["vocab"], "width": z["width"], "layers": layers, "norm": {"eps": 1e-5},
+            "loop": {"start": z["loop"][0], "stop": z["loop"][1], "times": z["loop"][2]}}
+
+
+def rutulix_runs(z):
+    return z["n_layers"] + (z["loop"][1] - z["loop"][0]) * (z["loop"][2] - 1)
+
+
+def closest_desarax(z):
+    """The closest layer-list model to a Rutulix size: latent-attention layers only, as many as the Rutulix model has layer runs,
+    same heads and mask size, routed GLU experts whose active matrices (top 2 x 3 matrices) match the dense pair."""
+    ff_e = max(64, (z["ff"] // 3) // 64 * 64)
+    return dict(width=z["width"], vocab=z["vocab"], pattern="a" * rutulix_runs(z), att_heads=z["att_heads"], att_dim=z["att_dim"],
+                att_vdim=z["att_dim"], kv_rank=z["kv_rank"], window=z["window"], experts=8, top=2, ff=ff_e, side=0,
+                heads=0, vdim=0, state=0, groups=1, conv=1)
+
+
+def mint_rutulix(dsk, torch, cfg, quant, chunk, context, device=0):
+    import hashlib
+    hc, specs = dsk.rutulix_from_config(cfg, quant=quant, max_seq_len=context, chunk=chunk)
+    m = dsk.Model(hc, 0, 1, device, layers=specs)
+    dev = torch.device("cuda", device)
+    W, V = cfg["width"], cfg["vocab"]
+
+    def up(name, shape, kind="mat"):
+        torch.manual_seed(int(hashlib.md5(name.encode()).hexdigest()[:8], 16))
+        if kind == "mat":
+            t = torch.randn(*shape, device=dev) * (shape[-1] ** -0.5)
+        elif kind == "embed":
+            t = torch.randn(*shape, device=dev)
+        elif kind == "norm":
+            t = 1.0 + 0.1 * torch.randn(*shape, device=dev)
+        elif kind == "talk":
+            t = torch.eye(shape[0], device=dev) + 0.1 * torch.randn(*shape, device=dev)
+        else:
+            t = 0.1 * torch.randn(*shape, device=dev)
+        t = t.to(torch.bfloat16).contiguous()
+        m.upload_device(name, "BF16", shape, t.data_ptr(), t.numel() * 2)
+        torch.cuda.synchronize()
+
+    up("embed", (V, W), "embed"); up("head", (V, W)); up("final.norm", (W,), "norm")
+    if hc.loop_times >= 1:
+        up("loop.step", (hc.loop_times, W), "small")
+    for i, lc in enumerate(cfg["layers"]):
+        p, mx = f"l{i}.", lc["mixer"]
+        HD, GD, ff = mx["heads"] * mx["dim"], mx["kv_heads"] * mx["dim"], lc["mlp"]["ff"]
+        for nm in ("norm1", "norm1b", "norm2", "norm2b"):
+            up(p + nm, (W,), "norm")
+        up(p + "mix.q", (HD, W)); up(p + "mix.k", (GD, W)); up(p + "mix.q.norm", (HD,), "norm"); up(p + "mix.k.norm", (GD,), "norm")
+        up(p + "mix.talk", (mx["heads"], mx["heads"]), "talk"); up(p + "mix.o", (W, HD))
+        up(p + "mlp.up", (ff, W)); up(p + "mlp.up.b", (ff,), "small"); up(p + "mlp.down", (W, ff)); up(p + "mlp.down.b", (W,), "small")
+        up(p + "mlp.act", (2,), "small")
+    m.finalize()
+    return m
+
+
+def rutulix_matrix_elements(cfg, z):
+    """Matrix elements one token multiplies with, and the attention's own multiply-adds per token at the mean number of visible
+    keys (half the mask size): scores and weighted values over all heads."""
+    W, mx = cfg["width"], cfg["layers"][0]["mixer"]
+    per = (mx["heads"] + mx["kv_heads"]) * mx["dim"] * W + W * mx["heads"] * mx["dim"] + 2 * z["ff"] * W
+    att = 2 * mx["heads"] * mx["dim"] * (z["window"] / 2.0)
+    return W * cfg["vocab"] + rutulix_runs(z) * per, rutulix_runs(z) * att
 
 
 def desarax_config(z):
@@ -37,8 +114,11 @@ def desarax_config(z):
             else:
                 last_a = i
             layers.append({"type": "latent_attention", "mlp": mlp, "mixer": mx})
-    return {"architecture": "Desarax", "vocab": z["vocab"], "width": z["width"], "layers": layers, "norm": {"eps": 1e-5, "groups": 4},
-            "residual_mult": 0.5, "logit_scale": 1.0, "token_side": {"dim": z["side"]}}
+    cfg = {"architecture": "Desarax", "vocab": z["vocab"], "width": z["width"], "layers": layers, "norm": {"eps": 1e-5, "groups": 4},
+           "residual_mult": 0.5, "logit_scale": 1.0}
+    if z["side"]:
+        cfg["token_side"] = {"dim": z["side"]}
+    return cfg
 
 
 def mint_desarax(dsk, torch, cfg, quant, chunk, context, device=0):
@@ -47,7 +127,7 @@ def mint_desarax(dsk, torch, cfg, quant, chunk, context, device=0):
     m = dsk.Model(hc, 0, 1, device, layers=specs)
     dev = torch.device("cuda", device)
     W, V, L = cfg["width"], cfg["vocab"], len(cfg["layers"])
-    sd = cfg["token_side"]["dim"]
+    sd = (cfg.get("token_side") or {}).get("dim", 0)
 
     def up(name, shape, kind="mat"):
         torch.manual_seed(int(hashlib.md5(name.encode()).hexdigest()[:8], 16))
@@ -67,7 +147,9 @@ def mint_desarax(dsk, torch, cfg, quant, chunk, context, device=0):
         m.upload_device(name, "BF16", shape, t.data_ptr(), t.numel() * 2)
         torch.cuda.synchronize()
 
-    up("embed", (V, W), "embed"); up("final.norm", (W,), "norm"); up("side.embed", (V, sd * L), "embed")
+    up("embed", (V, W), "embed"); up("final.norm", (W,), "norm")
+    if sd:
+        up("side.embed", (V, sd * L), "embed")
     for i, lc in enumerate(cfg["layers"]):
         p, mx = f"l{i}.", lc["mixer"]
         up(p + "norm1", (W,), "norm")
@@ -85,7 +167,8 @@ def mint_desarax(dsk, torch, cfg, quant, chunk, context, device=0):
         up(p + "mlp.router", (E, W)); up(p + "mlp.correction", (E,), "small")
         for e in range(E):
             up(f"{p}mlp.e{e}.gate", (ff, W)); up(f"{p}mlp.e{e}.up", (ff, W)); up(f"{p}mlp.e{e}.down", (W, ff))
-        up(p + "side.gate", (sd, W)); up(p + "side.proj", (W, sd)); up(p + "side.norm", (W,), "norm")
+        if sd:
+            up(p + "side.gate", (sd, W)); up(p + "side.proj", (W, sd)); up(p + "side.norm", (W,), "norm")
     m.finalize()
     return m
 
@@ -102,7 +185,7 @@ def active_matrix_elements(cfg):
             H, D, Vd, R = mx["heads"], mx["dim"], mx["vdim"], mx["kv_rank"]
             n += H * D * W + H * (D + Vd) * R + W * H * Vd + (0 if "kv_from" in mx else R * W)
         n += 3 * lc["mlp"]["router"]["top"] * lc["mlp"]["expert"]["ff"] * W + lc["mlp"]["router"]["experts"] * W
-        n += 2 * cfg["token_side"]["dim"] * W
+        n += 2 * (cfg.get("token_side") or {}).get("dim", 0) * W
     return n
 
 
@@ -114,11 +197,60 @@ def peaks(repo):
         return 6650.0, 1590.0, "fallback"
 
 
+def measure_layer_list(m, label, vocab, flops_per_token, hbm, tfl, prompt_len, gen, chunk, log, extra=None):
+    """Prefill (host-timed synchronous call, best of 3 after a warm-up) and decode (device loop, CUDA events) of one model."""
+    rng = np.random.RandomState(0)
+    prompt = rng.randint(0, vocab, prompt_len).astype(np.int32)
+    m.forward_chunk(prompt, 0, [prompt_len - 1])                               # warm-up (also the first-use costs)
+    ts = []
+    for _ in range(3):
+        t0 = time.perf_counter()
+        m.forward_chunk(prompt, 0, [prompt_len - 1])
+        ts.append(time.perf_counter() - t0)
+    pre = prompt_len / min(ts)
+    m.decode_greedy(prompt_len, 8)                                             # captures the step graph
+    m.forward_chunk(prompt, 0, [prompt_len - 1])
+    toks, ms = m.decode_greedy(prompt_len, gen)
+    dec = gen / (ms * 1e-3)
+    ab = m.active_bytes_per_token()
+    r = {"model": label, "quant": "bf16", "resident_gb": m.resident_bytes() / 1e9, "prefill_tok_s": pre, "prefill_tokens": prompt_len, "chunk": chunk,
+         "decode_tok_s": dec, "decode_tokens": gen, "active_bytes_per_token": ab, "decode_frac_of_hbm": ab * dec / (hbm * 1e9),
+         "prefill_frac_of_bf16": flops_per_token * pre / (tfl * 1e12), "launches_per_token": m.launches_per_forward()}
+    r.update(extra or {})
+    log(json.dumps(r))
+    return r
+
+
+def run_rutulix(dsk, torch, name, hbm, tfl, prompt_len, gen, chunk, log):
+    """A Rutulix size and the closest layer-list model (Desarax, latent-attention layers) at equal size."""
+    z = SIZES[name]
+    cfg = rutulix_config(z)
+    t0 = time.time()
+    m = mint_rutulix(dsk, torch, cfg, "bf16", chunk, prompt_len + gen + 8)
+    log(f"hybrid/{name}/bf16: minted {m.resident_bytes() / 1e9:.2f} GB in {time.time() - t0:.1f} s")
+    mat, att = rutulix_matrix_elements(cfg, z)
+    res = [measure_layer_list(m, f"Rutulix {name}", z["vocab"], 2.0 * mat, hbm, tfl, prompt_len, gen, chunk, log,
+                              {"layer_runs": rutulix_runs(z), "width": z["width"], "attention_flops_per_token_fp32": 2.0 * att})]
+    m.close()
+    zd = closest_desarax(z)
+    cfgd = desarax_config(zd)
+    t0 = time.time()
+    m = mint_desarax(dsk, torch, cfgd, "bf16", chunk, prompt_len + gen + 8)
+    log(f"hybrid/{name}/closest Desarax/bf16: minted {m.resident_bytes() / 1e9:.2f} GB in {time.time() - t0:.1f} s")
+    res.append(measure_layer_list(m, f"Desarax latent-attention layers at {name}", z["vocab"], 2.0 * active_matrix_elements(cfgd), hbm, tfl, prompt_len,
+                                  gen, chunk, log, {"layers": len(cfgd["layers"]), "width": z["width"]}))
+    m.close()
+    return res
+
+
 def run(dsk, torch, repo, bench_module, sizes=("small", "v2lite_like"), prompt_len=2048, gen=128, chunk=2048, log=print):
     hbm, tfl, src = peaks(repo)
     out = {"peaks": {"hbm_gbs": hbm, "bf16_tflops": tfl, "source": src}, "results": []}
     for name in sizes:
         z = SIZES[name]
+        if z.get("design") == "Rutulix":
+            out["results"] += run_rutulix(dsk, torch, name, hbm, tfl, prompt_len, gen, chunk, log)
+            continue
         cfg = desarax_config(z)
         for quant in ("bf16",):
             t0 = time.time()

@@ -112,7 +112,7 @@ typedef struct dsk_hybrid_config {
   int tie_head;              /* 1: the LM head is the embedding table; 0: tensor "head" */
   int loop_start, loop_stop, loop_times;   /* layers loop_start .. loop_stop - 1 run loop_times times in a row with the same weights and a
                                               cache / state of their own per pass; tensor loop.step [times][dim]: row t is added to the
-                                              residual stream right before pass t.  loop_times <= 1 or an empty range: every layer once */
+                                              residual stream right before pass t (a loop of one pass still adds row 0).  loop_times 0: no loop */
 } dsk_hybrid_config;
 
 typedef struct dsk_model dsk_model;

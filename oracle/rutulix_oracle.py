@@ -8,7 +8,7 @@ rms(v) = v / sqrt(mean(v^2) + eps) * w.
 
   model:      x = E[token];  layer runs in order;  logits = Hd ln_final(x)
   layer loop: layers start .. stop-1 run `times` times with the same weights; a layer run has its own keys and values;
-              before pass t (also t = 0) x <- x + step[t]
+              before pass t (also t = 0, also when times = 1) x <- x + step[t]
   layer:      x <- x + ln_1b(att(ln_1(x)));  x <- x + ln_2b(ff(ln_2(x)))   (no second line when the layer has no feed-forward)
   attention:  q = rms_q(W_q h) over all heads' rows at once, k = rms_k(W_k h) likewise; value of the position = W_k h itself;
               in every head the first `dims` entries are rotated pairwise (2i, 2i+1) by pos * f_i, scaled by the magnitude m;
@@ -120,7 +120,7 @@ def dense_ff(W, p, h):
 def layer_runs(cfg):
     """[(layer, pass or None)]: pass is set on the run that opens a pass of the loop."""
     n, lp = len(cfg["layers"]), cfg.get("loop")
-    if not lp or lp["times"] <= 1 or lp["stop"] <= lp["start"]:
+    if not lp or lp["times"] < 1 or lp["stop"] <= lp["start"]:
         return [(i, None) for i in range(n)]
     runs = [(i, None) for i in range(lp["start"])]
     for t in range(lp["times"]):
@@ -170,7 +170,7 @@ def tensor_shapes(cfg):
     Wd, V = cfg["width"], cfg["vocab"]
     shapes = {"embed": (V, Wd), "final.norm": (Wd,), "head": (V, Wd)}
     lp = cfg.get("loop")
-    if lp and lp["times"] > 1 and lp["stop"] > lp["start"]:
+    if lp and lp["times"] >= 1:
         shapes["loop.step"] = (lp["times"], Wd)
     for i, lc in enumerate(cfg["layers"]):
         p, mx = f"l{i}.", lc["mixer"]

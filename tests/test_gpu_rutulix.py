@@ -335,7 +335,7 @@ def test_bad_configs_are_refused(ro):
 
 
 # ---- other sizes --------------------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("case", ["ones", "odd", "wide", "no_loop", "loop_inside", "loop_all"])
+@pytest.mark.parametrize("case", ["ones", "odd", "wide", "one_pass", "loop_inside", "loop_all"])
 def test_other_sizes(mk, ro, case):
     loop = None
     if case == "ones":      # every count that can be 1 is 1
@@ -348,10 +348,8 @@ def test_other_sizes(mk, ro, case):
     else:
         layers, width, vocab = [ro.att(heads=2, size=4, ff=12), ro.att(heads=3, dim=6, size=9), ro.att(heads=2, kv_heads=1, dim=10, size=6, ff=8),
                                 ro.att(heads=4, kv_heads=2, size=3, ff=10)], 36, 50
-        loop = {"no_loop": None, "loop_inside": (1, 3, 2), "loop_all": (0, 4, 2)}[case]
+        loop = {"one_pass": (2, 3, 1), "loop_inside": (1, 3, 2), "loop_all": (0, 4, 2)}[case]   # one pass: no repeat, but its pass vector
     cfg = ro.model_config(layers, width=width, vocab=vocab, loop=loop)
-    if case == "no_loop":
-        cfg["loop"] = {"start": 2, "stop": 3, "times": 1}      # a loop of one pass is no loop (and has no pass vector)
     m, W = mk(cfg, seed=31, chunk=16)
     toks = tokens_for(cfg, 45, 3)
     exp, exp_layers = ro.run(cfg, W, toks)

@@ -100,8 +100,8 @@ def test_rutulix_config_to_layer_specs(ro):
     assert (a.ff_kind, a.ff_hidden, a.ff_act) == (dsk.FF_DENSE, 28, dsk.ACT_XIELU) and abs(a.att_scale - 0.3) < 1e-7
     assert b.ff_kind == dsk.FF_NONE and b.rot_factor == 0.0 and b.rot_dims == 12       # no scaling: plain frequencies
     assert c.att_kv_heads == 1 and abs(c.rot_slow - 0.5) < 1e-7
-    cfg["loop"]["times"] = 1                                                           # one pass is no loop
-    assert dsk.rutulix_from_config(cfg)[0].loop_times == 1 and dsk.rutulix_from_config(cfg)[0].loop_stop == 0
+    del cfg["loop"]
+    assert dsk.rutulix_from_config(cfg)[0].loop_times == 0
     cfg["layers"][1]["type"] = "latent_attention"
     with pytest.raises(dsk.DskError):
         dsk.rutulix_from_config(cfg)
