@@ -1024,9 +1024,20 @@ __global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, con
   for (int j0 = lo; j0 <= hi; j0 += 32) {
     __syncthreads();
     if (tid < 32) rowoff[tid] = (j0 + tid) % ring;
-    for (int e = tid; e < 32 * GD; e += blockDim.x) {
-      const int jj = e / GD, r = e - jj * GD, j = j0 + jj;
-      ks[jj * (GD + 1) + r] = j <= hi ? kc[(size_t)(j % ring) * GD + r] : 0.f;
+    if ((GD & 3) == 0) {   // 16-byte loads, several in flight per thread (the rows are 16-byte aligned: GD * 4 bytes each)
+      const int GD4 = GD >> 2;
+#pragma unroll 8
+      for (int e = tid; e < 32 * GD4; e += 256) {
+        const int jj = e / GD4, r = (e - jj * GD4) * 4, j = j0 + jj;
+        const float4 v = j <= hi ? *reinterpret_cast<const float4*>(kc + (size_t)(j % ring) * GD + r) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float* d = ks + jj * (GD + 1) + r;
+        d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+      }
+    } else {
+      for (int e = tid; e < 32 * GD; e += blockDim.x) {
+        const int jj = e / GD, r = e - jj * GD, j = j0 + jj;
+        ks[jj * (GD + 1) + r] = j <= hi ? kc[(size_t)(j % ring) * GD + r] : 0.f;
+      }
     }
     __syncthreads();
     for (int h = w; h < H; h += 8) {   // raw scores: lane = key
