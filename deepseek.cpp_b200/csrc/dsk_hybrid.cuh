@@ -694,7 +694,7 @@ __global__ void __launch_bounds__(512) ssd_scan(const float* __restrict__ proj, 
 // key range is cut into NS shares over blockIdx.z and latent_swa_merge combines the partial results.
 // ---------------------------------------------------------------------------------------------------------------------
 // first position that position i sees: mask 0 is a sliding window of `size` positions (i included), mask 1 cuts the sequence
-// into chunks of `size` positions counted from position 0, and i sees its own chunk up to itself
+// into chunks of `size` positions (borders at multiples of `size`), and i sees its own chunk up to itself
 __host__ __device__ __forceinline__ int mask_first(int mask, int size, int i) {
   if (mask == 1) return (i / size) * size;
   return i - size + 1 > 0 ? i - size + 1 : 0;
@@ -939,7 +939,7 @@ __global__ void add_row(float* __restrict__ x, int ld, const float* __restrict__
 //   rot acts on the first rot_dims dimensions of every head: the pair (2i, 2i + 1) turns by the angle pos * freq[i], and cos / sin
 //   are multiplied by `mag`.  Positions and angles are fp32.
 // q goes to q_out; the prepared key goes to row pos % ring of kcache.  Values: with v_src == nullptr the value of a position is
-// its key projection as projected (before norm and rotation); otherwise v_src rows (same pitch as k) are cached.
+// the raw output of its key matrix (ahead of the norm and the rotation); otherwise v_src rows (same pitch as k) are cached.
 // ---------------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) qk_norm_rope(const float* __restrict__ q, float* __restrict__ q_out, int HD,
                                                     const float* __restrict__ k, const float* __restrict__ v_src, int GD, int GV,

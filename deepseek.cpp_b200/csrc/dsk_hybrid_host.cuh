@@ -15,7 +15,7 @@
 // A parallel block computes, with h = norm1(x):  x += m (mixer(h) + ff(h));  a sandwich block  x += norm1b(mixer(norm1(x))),
 // x += norm2b(ff(norm2(x))).  Then, when the model has a per-layer token table,
 // g = gelu_tanh(side.gate x) * side.embed[token][i*sd : (i+1)*sd],  y = side.proj g,  x += m * rmsnorm(y) * side.norm.
-// A layer loop repeats a range of layers with the same weights; every repeat ("layer run") has its own cache / state.
+// A layer loop repeats a range of layers with the same weights; each repetition ("layer run") keeps a separate cache / state.
 #pragma once
 
 namespace hyb {
@@ -146,7 +146,7 @@ static int validate(const dsk_hybrid_config& c, const dsk_layer_spec* L) {
     } else if (s.mixer == DSK_MIX_GQA) {
       if (s.att_heads <= 0 || s.att_kv_heads <= 0 || s.att_dim <= 0 || s.att_vdim <= 0 || s.att_window <= 0) return fail(-1, "layer %d: bad attention sizes", i);
       if (s.att_heads % s.att_kv_heads != 0) return fail(-1, "layer %d: heads %d not a multiple of kv_heads %d", i, s.att_heads, s.att_kv_heads);
-      if (s.att_vdim != s.att_dim) return fail(-1, "layer %d: the values are the key projection, so vdim %d must equal dim %d", i, s.att_vdim, s.att_dim);
+      if (s.att_vdim != s.att_dim) return fail(-1, "layer %d: values come out of the key matrix, so vdim %d must equal dim %d", i, s.att_vdim, s.att_dim);
       if (s.rot_dims < 0 || s.rot_dims > s.att_dim || s.rot_dims % 2 != 0) return fail(-1, "layer %d: rot dims %d must be even and at most dim %d", i, s.rot_dims, s.att_dim);
       if (s.rot_dims > 0 && !(s.rot_base > 0.f)) return fail(-1, "layer %d: bad rotation base", i);
       if (gqa_attn_smem_floats(s.att_heads, s.att_kv_heads, s.att_dim, s.att_vdim) * 4 > 200 * 1024)

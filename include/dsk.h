@@ -70,16 +70,16 @@ typedef struct dsk_config {
 enum { DSK_MIX_SSD = 0, DSK_MIX_LATENT_SWA = 1, DSK_MIX_GQA = 2 };
 enum { DSK_FF_NONE = 0, DSK_FF_MOE = 1, DSK_FF_DENSE = 2 };
 enum { DSK_MASK_WINDOW = 0,   /* position i sees j with 0 <= i - j < att_window */
-       DSK_MASK_CHUNK = 1 };  /* position i sees j <= i with floor(i / att_window) == floor(j / att_window), counted from position 0 */
+       DSK_MASK_CHUNK = 1 };  /* position i sees j <= i with floor(i / att_window) == floor(j / att_window): borders at multiples of att_window in sequence positions */
 enum { DSK_ACT_XIELU = 0 };   /* z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z/2;  (p, q) = tensor mlp.act */
 enum { DSK_BLOCK_PARALLEL = 0,   /* h = norm1(x); x += residual_mult (mixer(h) + ff(h)) */
        DSK_BLOCK_SANDWICH = 1 }; /* x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))) */
 enum { DSK_NORM_RMS = 0,         /* x / sqrt(mean(x^2) + eps) * w in norm_groups parts */
        DSK_NORM_LAYER = 1 };     /* (x - mean) / sqrt(mean((x - mean)^2) + eps) * w, no bias */
 /*   DSK_MIX_GQA         softmax attention with att_heads query heads over att_kv_heads cached key heads (query head h reads key head
- *                       h / (att_heads / att_kv_heads)); the values are the key projection itself, as projected (no value matrix:
+ *                       h / (att_heads / att_kv_heads)); a position's value vector is the raw output of its key matrix, taken ahead of the key norm and the rotation (no value matrix:
  *                       att_vdim == att_dim); RMS norm with a weight over the whole query projection and over the whole key
- *                       projection; rotary positions on the first rot_dims dimensions of every head, dimension 2i paired with 2i + 1,
+ *                       projection; rotary positions on the first rot_dims dimensions of every head, entries (2i, 2i + 1) of a head turning together,
  *                       frequencies base^(-2i/rot_dims) with YaRN scaling when rot_factor > 0 (ramp between the dimensions where
  *                       rot_original / wavelength = rot_fast and rot_slow; cos and sin times 0.1 ln(rot_factor) + 1); scores times
  *                       att_scale; with att_talk the heads' scores are mixed before the softmax (score_h <- sum_g T[h][g] score_g,
@@ -111,7 +111,7 @@ typedef struct dsk_hybrid_config {
   int norm_kind;             /* DSK_NORM_* of every norm outside the mixers */
   int tie_head;              /* 1: the LM head is the embedding table; 0: tensor "head" */
   int loop_start, loop_stop, loop_times;   /* layers loop_start .. loop_stop - 1 run loop_times times in a row with the same weights and a
-                                              cache / state of their own per pass; tensor loop.step [times][dim]: row t is added to the
+                                              separate cache / state for every repetition; tensor loop.step [times][dim]: row t is added to the
                                               residual stream right before pass t (a loop of one pass still adds row 0).  loop_times 0: no loop */
 } dsk_hybrid_config;
 

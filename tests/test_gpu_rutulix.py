@@ -324,7 +324,7 @@ def test_bad_configs_are_refused(ro):
     with pytest.raises(dsk.DskError):
         dsk.Model(hc, layers=sp)
     cfg = ro.model_config([ro.att()])
-    cfg["layers"][0]["mixer"]["vdim"] = 5                 # the values are the keys: another value size cannot be
+    cfg["layers"][0]["mixer"]["vdim"] = 5                 # values come out of the key matrix: a different value size is contradictory
     hc, sp = dsk.rutulix_from_config(cfg, quant="fp32")
     with pytest.raises(dsk.DskError):
         dsk.Model(hc, layers=sp)
