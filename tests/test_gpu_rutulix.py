@@ -72,7 +72,7 @@ def peaky(W):
 
 
 # ---- each mechanism alone -------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("kind", ["plain", "talk", "rotation", "rotation_full", "yarn", "grouped", "chunks", "ff", "loop"])
+@pytest.mark.parametrize("kind", ["plain", "talk", "rotation", "rotation_full", "yarn", "yarn_step", "grouped", "chunks", "ff", "loop"])
 def test_mechanism_alone(mk, ro, kind):
     """From one head group, no rotation, one chunk, identity head mixing, no feed-forward and no loop, one mechanism at a time."""
     a = dict(heads=3, kv_heads=3, dim=8, size=64, scale=0.3, dims=0, base=100.0)
@@ -85,6 +85,8 @@ def test_mechanism_alone(mk, ro, kind):
         a.update(dims=8, base=7.0)
     elif kind == "yarn":
         a.update(dims=6, base=300.0, scaling={"factor": 6.0, "original": 32, "fast": 6.0, "slow": 0.75})
+    elif kind == "yarn_step":      # both ends of the ramp fall on pair 0: the ramp is a step (the guard against a zero-length ramp)
+        a.update(dims=8, base=1000.0, scaling={"factor": 16.0, "original": 8, "fast": 32.0, "slow": 2.0})
     elif kind == "grouped":
         a.update(heads=6, kv_heads=2)
     elif kind == "chunks":
